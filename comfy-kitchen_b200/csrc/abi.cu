@@ -1,0 +1,94 @@
+// Library-wide entry points of libck_b200: error text, queries, tuning switches.
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ckb {
+
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_quant_variant{1};
+std::atomic<int> g_gemm_variant{0};
+
+char* last_error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(last_error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+namespace {
+struct DeviceInfo {
+    bool known = false;
+    int major = 0, minor = 0, sms = 0;
+};
+std::mutex g_dev_mutex;
+DeviceInfo g_dev[64];
+}  // namespace
+
+int check_device(int* sm_count_out) {
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+    DeviceInfo info;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!g_dev[dev].known) {
+            CKB_CUDA_OK(cudaDeviceGetAttribute(&g_dev[dev].major, cudaDevAttrComputeCapabilityMajor, dev));
+            CKB_CUDA_OK(cudaDeviceGetAttribute(&g_dev[dev].minor, cudaDevAttrComputeCapabilityMinor, dev));
+            CKB_CUDA_OK(cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+            g_dev[dev].known = true;
+        }
+        info = g_dev[dev];
+    }
+    if (info.major != 10)
+        return fail(CK_B200_ERR_UNSUPPORTED_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                    info.major, info.minor);
+    if (sm_count_out) *sm_count_out = info.sms;
+    return CK_B200_OK;
+}
+
+}  // namespace ckb
+
+extern "C" {
+
+const char* ck_b200_last_error(void) { return ckb::last_error_buffer(); }
+
+int64_t ck_b200_query(int what) {
+    switch (what) {
+        case CK_B200_QUERY_ABI_VERSION: return 1;
+        case CK_B200_QUERY_SM_COUNT: {
+            int sms = 0;
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+            return sms;
+        }
+        case CK_B200_QUERY_WORKSPACE_BYTES: return 64ll << 20;
+        case CK_B200_QUERY_COMPUTE_CAPABILITY: {
+            int dev = 0, major = 0, minor = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+            if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return -1;
+            if (cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess) return -1;
+            return major * 10 + minor;
+        }
+        case CK_B200_QUERY_GEMM_LAUNCHES: return ckb::g_launches.load();
+        default: return -1;
+    }
+}
+
+int ck_b200_set_tuning(int key, int value) {
+    switch (key) {
+        case CK_B200_TUNE_QUANT_VARIANT: return ckb::g_quant_variant.exchange(value);
+        case CK_B200_TUNE_GEMM_VARIANT: return ckb::g_gemm_variant.exchange(value);
+        default: return -1;
+    }
+}
+
+}  // extern "C"

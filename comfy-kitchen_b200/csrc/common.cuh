@@ -1,0 +1,68 @@
+// Shared host/device helpers of libck_b200: error reporting, launch accounting, PTX wrappers (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/ck_b200.h"
+
+namespace ckb {
+
+// ---- host side --------------------------------------------------------------------------------
+
+// Per-thread message of the last failure, returned by ck_b200_last_error().
+char* last_error_buffer();
+int fail(int code, const char* fmt, ...);
+// Number of kernels this library has launched in this process.
+extern std::atomic<long long> g_launches;
+// Tuning switches (ck_b200_set_tuning).
+extern std::atomic<int> g_quant_variant;
+extern std::atomic<int> g_gemm_variant;
+
+// Checks that the current device is compute capability 10.x (cached per device ordinal).
+int check_device(int* sm_count_out);
+
+#define CKB_CUDA_OK(expr)                                                                              \
+    do {                                                                                               \
+        cudaError_t e__ = (expr);                                                                      \
+        if (e__ != cudaSuccess)                                                                        \
+            return ::ckb::fail(CK_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));     \
+    } while (0)
+
+static inline int64_t round_up64(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+static inline int64_t ceil_div64(int64_t x, int64_t m) { return (x + m - 1) / m; }
+
+// ---- device side ------------------------------------------------------------------------------
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Byte offset of logical scale (r, c) in the 128x4 tiled scale tensor with cbg_count groups of 4 columns.
+__device__ __forceinline__ int64_t sf_offset(int64_t r, int c, int cbg_count) {
+    int64_t rb = r >> 7;
+    int rem = (int)(r & 127);
+    return ((rb * cbg_count + (c >> 2)) * 32 + (rem & 31)) * 16 + (rem >> 5) * 4 + (c & 3);
+}
+
+// 16-byte streaming load through the read-only path, not allocating in L1.
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ckb

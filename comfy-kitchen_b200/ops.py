@@ -1,0 +1,199 @@
+"""Host side of the NVFP4 linear path: the three operators of the reference backend interface.
+
+Names, parameters, defaults, returned shapes and error behaviour mirror the reference CUDA backend
+(``comfy_kitchen/backends/cuda/__init__.py:582-667`` and ``:1725-1849``); results are bit-identical to the
+reference *eager* backend for quantize/dequantize.  PyTorch is used for allocation, device and stream
+handling only; the arithmetic runs in the kernels of ``libck_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+DTYPE_TO_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}  # eager/quantization.py:34-42
+
+
+def roundup(x: int, multiple: int) -> int:
+    return ((x + multiple - 1) // multiple) * multiple
+
+
+def _plain(t):
+    return t.data if isinstance(t, torch.nn.Parameter) else t
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _scale_on(device: torch.device, s: torch.Tensor) -> torch.Tensor:
+    s = _plain(s)
+    if s.dtype != torch.float32:
+        raise TypeError(f"per-tensor scale must be float32, got {s.dtype}")
+    if s.numel() != 1:
+        raise ValueError("per-tensor scale must have exactly one element")
+    if s.device != device:
+        s = s.to(device, non_blocking=True)
+    return s.reshape(1) if s.is_contiguous() else s.contiguous().reshape(1)
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor (comfy_kitchen_b200 has no CPU path), got {t.device}")
+
+
+def quantize_nvfp4(x: torch.Tensor, per_tensor_scale: torch.Tensor, epsilon: float = 0.0, pad_16x: bool = False,
+                   hi_first: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16/fp16/fp32 [R, C] -> (packed e2m1 uint8 [R', C'/2], e4m3 block scales [roundup(R',128), roundup(C'/16,4)]
+    in the 128x4 tiled layout).  ``epsilon`` is accepted and unused, as in every reference backend."""
+    x = _plain(x)
+    _require_cuda(x, "x")
+    if x.dim() != 2:
+        raise ValueError(f"quantize_nvfp4 needs a 2D tensor, got {x.dim()}D")
+    if x.dtype not in DTYPE_TO_CODE:
+        raise TypeError(f"quantize_nvfp4: unsupported dtype {x.dtype}")
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    orig_rows, orig_cols = x.shape
+    if pad_16x:
+        num_rows, num_cols = roundup(orig_rows, 16), roundup(orig_cols, 16)
+    else:
+        num_rows, num_cols = orig_rows, orig_cols
+        assert num_rows % 16 == 0, f"num_rows must be divisible by 16, got {num_rows}"
+        assert num_cols % 16 == 0, f"num_cols must be divisible by 16, got {num_cols}"
+    with torch.cuda.device(x.device):
+        pts = _scale_on(x.device, per_tensor_scale)
+        qx = torch.empty((num_rows, num_cols // 2), device=x.device, dtype=torch.uint8)
+        # the kernel writes every byte of the scale tensor, zero padding included: no memset pass
+        sx = torch.empty((roundup(num_rows, 128), roundup(num_cols // 16, 4)), device=x.device, dtype=torch.uint8)
+        if qx.numel() == 0:
+            return qx, sx.view(torch.float8_e4m3fn)
+        rc = _lib.load().ck_b200_quantize_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(pts), _ptr(qx), _ptr(sx), orig_rows,
+                                                orig_cols, int(bool(pad_16x)), int(bool(hi_first)), _stream(x.device))
+    _lib.check(rc, "quantize_nvfp4")
+    return qx, sx.view(torch.float8_e4m3fn)
+
+
+def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_scales: torch.Tensor,
+                     output_type: torch.dtype = torch.bfloat16, hi_first: bool = True) -> torch.Tensor:
+    """packed uint8 [R, C/2] + tiled e4m3 scales -> [R, C] in ``output_type``."""
+    qx = _plain(qx)
+    block_scales = _plain(block_scales)
+    _require_cuda(qx, "qx")
+    if qx.dim() != 2 or qx.dtype != torch.uint8:
+        raise TypeError("dequantize_nvfp4 needs a 2D uint8 tensor")
+    if output_type not in DTYPE_TO_CODE:
+        raise TypeError(f"dequantize_nvfp4: unsupported output dtype {output_type}")
+    assert qx.is_contiguous(), "Input tensor must be contiguous"
+    num_rows, packed = qx.shape
+    want = (roundup(num_rows, 128), roundup(packed * 2 // 16, 4))
+    if block_scales.numel() != want[0] * want[1] or block_scales.element_size() != 1:
+        raise ValueError(f"block_scales must hold {want[0]}x{want[1]} one-byte scales, got {tuple(block_scales.shape)}")
+    assert block_scales.is_contiguous() and block_scales.device == qx.device
+    with torch.cuda.device(qx.device):
+        pts = _scale_on(qx.device, per_tensor_scale)
+        out = torch.empty((num_rows, packed * 2), device=qx.device, dtype=output_type)
+        if out.numel() == 0:
+            return out
+        rc = _lib.load().ck_b200_dequantize_nvfp4(_ptr(qx), _ptr(pts), _ptr(block_scales), _ptr(out),
+                                                  DTYPE_TO_CODE[output_type], num_rows, packed, int(bool(hi_first)),
+                                                  _stream(qx.device))
+    _lib.check(rc, "dequantize_nvfp4")
+    return out
+
+
+def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tensor, tensor_scale_b: torch.Tensor,
+                    block_scale_a: torch.Tensor, block_scale_b: torch.Tensor, bias: torch.Tensor | None = None,
+                    out_dtype: torch.dtype | None = None, alpha: torch.Tensor | None = None) -> torch.Tensor:
+    """[M, K/2] x [N, K/2]^T packed e2m1 with per-16 e4m3 block scales -> [M, N] in ``out_dtype`` (default bf16).
+    ``alpha``, when given, replaces tensor_scale_a * tensor_scale_b."""
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    _require_cuda(a, "a")
+    if out_dtype is None:
+        out_dtype = torch.bfloat16
+    if out_dtype not in DTYPE_TO_CODE:
+        raise TypeError(f"scaled_mm_nvfp4: unsupported out_dtype {out_dtype}")
+    if a.dim() != 2 or b.dim() != 2 or a.dtype != torch.uint8 or b.dtype != torch.uint8:
+        raise TypeError("scaled_mm_nvfp4 needs 2D uint8 operands")
+    m, k_a = a.shape
+    n, k_b = b.shape
+    assert k_a == k_b, "Matrix dimensions do not match"
+    k = 2 * k_a
+    assert a.is_contiguous() and b.is_contiguous(), "operands must be contiguous"
+    assert n % 8 == 0, "B tensor must have 8 alignment in N dimension"
+    assert block_scale_a.dtype == block_scale_b.dtype, "A and B scale dtype must match"
+    if block_scale_a.dtype not in (torch.float8_e4m3fn, torch.uint8):
+        raise ValueError(f"Unsupported scale dtype: {block_scale_a.dtype}")
+    sk = roundup(k // 16, 4)
+    assert block_scale_a.dim() == 2 and tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert block_scale_b.dim() == 2 and tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    assert block_scale_a.is_contiguous() and block_scale_b.is_contiguous(), "scales must be contiguous"
+    for t, nm in ((b, "b"), (block_scale_a, "block_scale_a"), (block_scale_b, "block_scale_b")):
+        if t.device != a.device:
+            raise TypeError(f"{nm} must be on {a.device}, got {t.device}")
+    bias_code = 2
+    if bias is not None and bias.numel() > 0:
+        bias = _plain(bias)
+        assert bias.dtype in (torch.float16, torch.bfloat16), "Only fp16 and bfloat16 bias are supported."
+        assert bias.numel() == n and bias.is_contiguous() and bias.device == a.device, "bias must be a contiguous [N] tensor"
+        bias_code = DTYPE_TO_CODE[bias.dtype]
+    else:
+        bias = None
+    with torch.cuda.device(a.device):
+        alpha_t = None
+        tsa = tsb = None
+        if alpha is not None:
+            alpha_t = _plain(alpha)
+            if alpha_t.dtype != torch.float32:
+                alpha_t = alpha_t.to(torch.float32)
+            alpha_t = _scale_on(a.device, alpha_t)
+        else:
+            tsa = _scale_on(a.device, tensor_scale_a)
+            tsb = _scale_on(a.device, tensor_scale_b)
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+        if out.numel() == 0:
+            return out
+        rc = _lib.load().ck_b200_scaled_mm_nvfp4(_ptr(a), _ptr(block_scale_a), _ptr(b), _ptr(block_scale_b), _ptr(tsa),
+                                                 _ptr(tsb), _ptr(alpha_t), _ptr(bias), bias_code, _ptr(out),
+                                                 DTYPE_TO_CODE[out_dtype], m, n, k, None, 0, _stream(a.device))
+    _lib.check(rc, "scaled_mm_nvfp4")
+    return out
+
+
+def dynamic_scale_nvfp4(x: torch.Tensor) -> torch.Tensor:
+    """amax(|x|)/(448*6) evaluated in x's dtype and returned as a float32 scalar tensor on x's device: the
+    per-tensor scale ``TensorCoreNVFP4Layout.quantize`` computes when none is given
+    (``comfy_kitchen/tensor/nvfp4.py:66-71``), without the host round trip."""
+    x = _plain(x)
+    _require_cuda(x, "x")
+    if x.dtype not in DTYPE_TO_CODE:
+        raise TypeError(f"dynamic_scale_nvfp4: unsupported dtype {x.dtype}")
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    with torch.cuda.device(x.device):
+        out = torch.empty((), device=x.device, dtype=torch.float32)
+        rc = _lib.load().ck_b200_dynamic_scale_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], x.numel(), _ptr(out),
+                                                     _stream(x.device))
+    _lib.check(rc, "dynamic_scale_nvfp4")
+    return out
+
+
+def set_tuning(key: int, value: int) -> int:
+    return int(_lib.load().ck_b200_set_tuning(key, value))
+
+
+def launches() -> int:
+    """Kernels this library has launched in this process."""
+    return int(_lib.load().ck_b200_query(_lib.QUERY_LAUNCHES))
+
+
+def read_device_status() -> int:
+    """Synchronises and returns the device status word (0 = no bounded wait ran out), clearing it."""
+    v = ctypes.c_int(0)
+    _lib.load().ck_b200_read_device_status(ctypes.byref(v))
+    return int(v.value)

@@ -1,0 +1,104 @@
+"""N-sharded (column-parallel) NVFP4 linear over ``torch.distributed``: one process per GPU.
+
+The reference is single-GPU; this is the multi-GPU form of its NVFP4 linear
+(``samples/nvfp4_linear.py:39-80``: quantize the activation, ``F.linear`` on two NVFP4 tensors).  Each
+rank keeps rows ``[n0, n1)`` of the weight resident as packed e2m1 bytes with its own tiled scale tensor;
+the per-tensor weight scale is computed once from the whole weight so that every rank's columns equal the
+columns of the unsharded result.  The activation is replicated; every rank quantizes it, multiplies by its
+shard and the bf16 column blocks are exchanged with one all-gather (NCCL over NVLink on GPUs, gloo in
+the CPU tests of the host logic).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(n: int, world: int, rank: int, unit: int = 8) -> tuple[int, int]:
+    """Rows [n0, n1) of an N-row weight owned by ``rank``: contiguous, in units of 8 rows (the N % 8 rule of
+    scaled_mm_nvfp4), sizes differing by at most one unit."""
+    if n % unit:
+        raise ValueError(f"N = {n} must be a multiple of {unit}")
+    u = n // unit
+    return (rank * u // world) * unit, ((rank + 1) * u // world) * unit
+
+
+class ShardedNVFP4Linear:
+    """y = x @ W^T + bias with W quantized to NVFP4 and sharded along N.
+
+    ``ops`` is a namespace with ``quantize_nvfp4``, ``scaled_mm_nvfp4`` and ``dynamic_scale_nvfp4`` (this package's
+    operators on GPUs; the CPU tests pass a stand-in so that the sharding and gather logic runs under gloo).
+    """
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, *, group=None, ops=None,
+                 input_scale: torch.Tensor | None = None, weight_scale: torch.Tensor | None = None):
+        if ops is None:
+            from . import ops as _ops
+            ops = _ops
+        self.ops = ops
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.out_features, self.in_features = weight.shape
+        self.n0, self.n1 = shard_rows(self.out_features, self.world, self.rank)
+        # global per-tensor scale, evaluated in the weight's dtype like TensorCoreNVFP4Layout.quantize does
+        if weight_scale is None:
+            weight_scale = ops.dynamic_scale_nvfp4(weight)
+        self.weight_scale = weight_scale.to(torch.float32).reshape(())
+        shard = weight[self.n0:self.n1].contiguous()
+        pad = shard.shape[0] % 16 != 0 or shard.shape[1] % 16 != 0
+        self.qweight, self.weight_block_scale = ops.quantize_nvfp4(shard, self.weight_scale, pad_16x=pad)
+        self.local_rows = shard.shape[0]
+        # pad_16x may have added rows; the GEMM takes N = local_rows (a multiple of 8) and the scale tensor is
+        # padded to 128 rows either way
+        self.qweight = self.qweight[: self.local_rows].contiguous()
+        self.bias = None if bias is None else bias[self.n0:self.n1].contiguous()
+        self.input_scale = input_scale
+
+    def local(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's [M, n1-n0] block of the output."""
+        ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
+        pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
+        qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
+        y = self.ops.scaled_mm_nvfp4(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
+                                     bias=self.bias, out_dtype=x.dtype if x.dtype != torch.float32 else torch.bfloat16)
+        return y[: x.shape[0], : self.local_rows]
+
+    def gather(self, y_local: torch.Tensor, row_major: bool = True) -> torch.Tensor:
+        """All-gather the column blocks.  ``row_major=False`` returns the rank-major [G, M, N/G] buffer the
+        collective produces (equal shards only) and skips the re-layout pass."""
+        if self.world == 1:
+            return y_local
+        m = y_local.shape[0]
+        sizes = [b - a for a, b in (shard_rows(self.out_features, self.world, r) for r in range(self.world))]
+        y_local = y_local.contiguous()
+        if len(set(sizes)) == 1:
+            flat = torch.empty((self.world * m, sizes[0]), dtype=y_local.dtype, device=y_local.device)
+            dist.all_gather_into_tensor(flat, y_local, group=self.group)
+            buf = flat.view(self.world, m, sizes[0])
+            if not row_major:
+                return buf
+            return buf.permute(1, 0, 2).reshape(m, self.out_features)
+        # unequal shards (e.g. 13824 columns over 8 ranks): pad every block to the widest, gather, drop the padding
+        widest = max(sizes)
+        padded = torch.zeros((m, widest), dtype=y_local.dtype, device=y_local.device)
+        padded[:, : y_local.shape[1]] = y_local
+        flat = torch.empty((self.world * m, widest), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(flat, padded, group=self.group)
+        buf = flat.view(self.world, m, widest)
+        return torch.cat([buf[r, :, : sizes[r]] for r in range(self.world)], dim=1)
+
+    def __call__(self, x: torch.Tensor, row_major: bool = True) -> torch.Tensor:
+        return self.gather(self.local(x), row_major=row_major)
+
+
+def replicated_from_seed(shape: tuple[int, int], seed: int, std: float, dtype: torch.dtype, device,
+                         transform: Callable[[torch.Tensor], torch.Tensor] | None = None) -> torch.Tensor:
+    """Same tensor on every rank: generated on the CPU from a seeded generator, then moved."""
+    g = torch.Generator().manual_seed(seed)
+    t = torch.randn(shape, generator=g, dtype=torch.float32) * std
+    if transform is not None:
+        t = transform(t)
+    return t.to(dtype).to(device)

@@ -1,0 +1,121 @@
+/*
+ * C ABI of libck_b200.so: the NVFP4 linear path (quantize_nvfp4, dequantize_nvfp4, scaled_mm_nvfp4)
+ * for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a native binding of comfy-kitchen would call in place of the reference's
+ * extern "C" launchers.  Every pointer named *_dev is device memory on the current CUDA device;
+ * `stream` is a cudaStream_t passed as void*.  Calls only enqueue work: they never synchronise,
+ * never allocate device memory and may be captured in a CUDA graph.  Every function returns 0 on
+ * success and a non-zero CK_B200_ERR_* code otherwise; nothing throws across this boundary and the
+ * message for the calling thread's last failure is available from ck_b200_last_error().
+ *
+ * Dtype codes follow the reference table (comfy_kitchen/backends/eager/quantization.py:34-42,
+ * comfy_kitchen/backends/cuda/dtype_dispatch.cuh:36-42): 0 = float32, 1 = float16, 2 = bfloat16.
+ */
+#ifndef CK_B200_H_
+#define CK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CK_B200_DTYPE_F32 0
+#define CK_B200_DTYPE_F16 1
+#define CK_B200_DTYPE_BF16 2
+
+#define CK_B200_OK 0
+#define CK_B200_ERR_INVALID_ARGUMENT 1 /* shape / alignment / dtype rejected before any launch */
+#define CK_B200_ERR_CUDA 2             /* a CUDA runtime or driver call failed */
+#define CK_B200_ERR_UNSUPPORTED_DEVICE 3 /* the current device is not compute capability 10.x */
+#define CK_B200_ERR_DEVICE_STATUS 4    /* a kernel reported a bounded wait that ran out */
+
+/*
+ * Block-quantize a row-major [rows, cols] matrix to NVFP4.
+ * Replaces launch_quantize_nvfp4_kernel (comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:323-384);
+ * arithmetic follows the eager backend bit for bit (comfy_kitchen/backends/eager/quantization.py:118-163).
+ *
+ *   x_dev                 [rows, cols] contiguous, dtype code x_dtype (0/1/2)
+ *   per_tensor_scale_dev  one float32
+ *   pad_16x               non-zero: rows and cols are zero-padded up to multiples of 16 (prow, pcol);
+ *                         zero: rows and cols must already be multiples of 16
+ *   q_out_dev             uint8 [prow, pcol/2]; element 2i in the high nibble when hi_first != 0
+ *   sf_out_dev            e4m3 bytes [roundup(prow,128), roundup(pcol/16,4)] in the 128x4 tiled layout
+ *                         (comfy_kitchen/float_utils.py:292-326); the kernel writes the zero padding itself
+ */
+int ck_b200_quantize_nvfp4(const void* x_dev, int x_dtype, const float* per_tensor_scale_dev, void* q_out_dev,
+                           void* sf_out_dev, int64_t rows, int64_t cols, int pad_16x, int hi_first, void* stream);
+
+/*
+ * Inverse of the above.  Replaces launch_dequantize_nvfp4_kernel
+ * (comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:386-435); rounding follows the eager backend
+ * (two roundings to the output dtype, comfy_kitchen/backends/eager/quantization.py:174-222).
+ *
+ *   q_dev    uint8 [rows, packed_cols];  sf_dev  e4m3 bytes [roundup(rows,128), roundup(packed_cols/8,4)] tiled
+ *   out_dev  [rows, 2*packed_cols] of dtype code out_dtype (0/1/2).  packed_cols must be a multiple of 8.
+ */
+int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tensor_scale_dev, const void* sf_dev,
+                             void* out_dev, int out_dtype, int64_t rows, int64_t packed_cols, int hi_first,
+                             void* stream);
+
+/*
+ * out[M,N] = out_dtype( alpha * (A . B^T with per-16 e4m3 block scales) + bias ), fp32 accumulation,
+ * alpha = *tensor_scale_a_dev * *tensor_scale_b_dev unless alpha_dev_or_null is given.
+ * Replaces launch_cublas_gemm_blockwise_fp4_kernel (comfy_kitchen/backends/cuda/ops/cublas_gemm_nvfp4.cu:295-340),
+ * i.e. the cuBLASLt call behind scaled_mm_nvfp4 (comfy_kitchen/backends/eager/quantization.py:225-249).
+ *
+ *   a_dev [M, K/2], b_dev [N, K/2] packed e2m1 (both with the same nibble order), 16-byte aligned
+ *   sfa_dev [roundup(M,128), roundup(K/16,4)], sfb_dev [roundup(N,128), roundup(K/16,4)] tiled e4m3 bytes
+ *   bias_dev_or_null [N] of dtype code bias_dtype (1 or 2; 0 also accepted)
+ *   out_dev [M, N] row-major of dtype code out_dtype (1 or 2; 0 also accepted)
+ *   K % 32 == 0 and N % 8 == 0 (the reference's constraints, comfy_kitchen/backends/cuda/__init__.py:1779,3621-3625)
+ *   workspace_dev / workspace_bytes: scratch for split-K reductions; may be NULL / 0, in which case
+ *   shapes that would use split-K run unsplit.  ck_b200_query(CK_B200_QUERY_WORKSPACE_BYTES) gives a
+ *   size that is always enough.
+ */
+int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                            const float* tensor_scale_a_dev, const float* tensor_scale_b_dev,
+                            const float* alpha_dev_or_null, const void* bias_dev_or_null, int bias_dtype,
+                            void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace_dev,
+                            size_t workspace_bytes, void* stream);
+
+/*
+ * amax(|x|) / (448*6) computed in the input dtype and widened to float32, the per-tensor scale
+ * TensorCoreNVFP4Layout.quantize derives when the caller gives none (comfy_kitchen/tensor/nvfp4.py:66-71).
+ * scale_out_dev receives one float32.  Two launches on `stream` (reduce, finalise); no host sync.
+ */
+int ck_b200_dynamic_scale_nvfp4(const void* x_dev, int x_dtype, int64_t numel, float* scale_out_dev, void* stream);
+
+/* Message describing the calling thread's last failure ("" if none).  Counterpart of the
+ * std::runtime_error text of the reference launchers (comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:380-383). */
+const char* ck_b200_last_error(void);
+
+#define CK_B200_QUERY_ABI_VERSION 0
+#define CK_B200_QUERY_SM_COUNT 1          /* of the current device */
+#define CK_B200_QUERY_WORKSPACE_BYTES 2   /* split-K workspace that is always enough */
+#define CK_B200_QUERY_COMPUTE_CAPABILITY 3 /* major*10 + minor of the current device */
+#define CK_B200_QUERY_GEMM_LAUNCHES 4     /* kernels launched by this library in this process (all entry points) */
+/* Small integer facts about the library / current device; -1 for an unknown key.  Counterpart of the
+ * module attributes of the reference extension (comfy_kitchen/backends/cuda/dlpack_bindings.cpp:3738). */
+int64_t ck_b200_query(int what);
+
+/*
+ * Device-side status word of the current device: 0 when no kernel of this library gave up on a bounded
+ * wait since the last call, otherwise a code naming the wait.  Synchronises the device; meant for tests
+ * and debugging (the reference has no counterpart: its GEMM is a library call).
+ */
+int ck_b200_read_device_status(int* status_out);
+
+/* Tuning switches used by tests and benchmarks to select kernel variants: key/value integers,
+ * returns the previous value or -1 for an unknown key.  No counterpart in the reference (its
+ * environment switches, comfy_kitchen/backends/cuda/__init__.py:212-215, do not touch this path). */
+#define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions everywhere, 1 = shared-reciprocal exact division (default) */
+#define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic */
+int ck_b200_set_tuning(int key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CK_B200_H_ */

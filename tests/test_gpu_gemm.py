@@ -1,0 +1,181 @@
+"""GPU parity of scaled_mm_nvfp4 (through the C ABI) against the CPU oracle (dequantize -> fp32 matmul), the
+reference golden vectors and, at full BASELINE sizes, torch's cuBLASLt NVFP4 matmul on the same operands.
+
+Tolerance (floating point): relative RMS error <= 1e-2 against the reference path on identical quantized
+operands; in practice the error is bf16 output rounding (~2e-3)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import amax_scale, from_bits, seeded_randn, to_bits
+
+pytestmark = pytest.mark.gpu
+REL_RMS_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ckb():
+    import comfy_kitchen_b200 as m
+    assert torch.cuda.is_available()
+    return m
+
+
+@pytest.fixture(params=[1, 2], ids=["bn128", "bn256"])
+def variant(request, ckb):
+    prev = ckb.set_tuning(1, request.param)
+    yield request.param
+    ckb.set_tuning(1, prev)
+    assert ckb.read_device_status() == 0, "a bounded wait ran out inside the GEMM kernel"
+
+
+def rel_rms(y, ref):
+    y, ref = y.double(), ref.double()
+    return float(((y - ref).pow(2).mean().sqrt()) / ref.pow(2).mean().sqrt().clamp_min(1e-30))
+
+
+def quantized_operands(ckb, M, N, K, seed, outliers=False):
+    x = seeded_randn((M, K), seed=seed, outlier_cols=max(1, K // 1000) if outliers else 0).cuda()
+    w = seeded_randn((N, K), seed=seed + 1, std=0.02).cuda()
+    tsx, tsw = amax_scale(x).cuda(), amax_scale(w).cuda()
+    padx = M % 16 != 0
+    qx, sfx = ckb.quantize_nvfp4(x, tsx, pad_16x=padx)
+    qw, sfw = ckb.quantize_nvfp4(w, tsw, pad_16x=N % 16 != 0)
+    qw = qw[:N].contiguous()      # the scale tensor is padded to 128 rows either way
+    return x, w, qx, sfx, tsx, qw, sfw, tsw
+
+
+def torch_scaled_mm(qx, sfx, tsx, qw, sfw, tsw, bias=None, out_dtype=torch.bfloat16):
+    """cuBLASLt NVFP4 through torch on the same operands: what the reference eager backend calls
+    (comfy_kitchen/backends/eager/quantization.py:225-249, comfy_kitchen/scaled_mm_v2.py:113-126)."""
+    from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+    return scaled_mm(
+        qx.view(torch.float4_e2m1fn_x2), qw.view(torch.float4_e2m1fn_x2).t(),
+        scale_a=[sfx.view(-1), tsx.reshape(())], scale_b=[sfw.view(-1), tsw.reshape(())],
+        scale_recipe_a=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+        scale_recipe_b=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+        swizzle_a=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
+        swizzle_b=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
+        bias=bias, output_dtype=out_dtype)
+
+
+@pytest.mark.parametrize("name", ["gemm_64x128x256", "gemm_48x72x96"])
+def test_gemm_golden(name, golden, ckb, variant):
+    qa = torch.from_numpy(golden[f"{name}/qa"].copy()).cuda()
+    qb = torch.from_numpy(golden[f"{name}/qb"].copy()).cuda()
+    sfa = torch.from_numpy(golden[f"{name}/sfa"].copy()).cuda().view(torch.float8_e4m3fn)
+    sfb = torch.from_numpy(golden[f"{name}/sfb"].copy()).cuda().view(torch.float8_e4m3fn)
+    tsa, tsb = (torch.tensor(float(v), dtype=torch.float32).cuda() for v in golden[f"{name}/ts"])
+    bias = from_bits(golden[f"{name}/bias"], 2).cuda() if f"{name}/bias" in golden else None
+    y = ckb.scaled_mm_nvfp4(qa, qb, tsa, tsb, sfa, sfb, bias=bias, out_dtype=torch.bfloat16)
+    ref = from_bits(golden[f"{name}/y"], 2)
+    assert y.shape == ref.shape and y.dtype == torch.bfloat16
+    assert rel_rms(y.cpu().float(), ref.float()) <= REL_RMS_TOL
+
+
+SMALL = [(256, 1024, 1024), (128, 128, 256), (16, 8, 32), (100, 200, 96), (129, 136, 320), (384, 264, 1024),
+         (1, 4096, 4096), (16, 10240, 4096), (64, 4096, 10240), (512, 1024, 2048), (300, 520, 2080)]
+
+
+@pytest.mark.parametrize("mnk", SMALL, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
+def test_gemm_vs_oracle(mnk, with_bias, ckb, oracle, variant):
+    M, N, K = mnk
+    if M * N * K > 3e9:
+        pytest.skip("too large for the CPU oracle")
+    Mp = (M + 15) // 16 * 16
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=M + N + K)
+    bias = seeded_randn((1, N), seed=99, std=0.5).reshape(N).cuda() if with_bias else None
+    y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias, out_dtype=torch.bfloat16)
+    assert tuple(y.shape) == (Mp, N)
+    ref = oracle.scaled_mm_nvfp4(to_bits(qx), to_bits(qw), float(tsx), float(tsw), to_bits(sfx), to_bits(sfw),
+                                 bias=None if bias is None else to_bits(bias))
+    ref = from_bits(ref, 2).float()
+    got = y.cpu().float()
+    assert torch.isfinite(got).all()
+    assert rel_rms(got[:M], ref[:M]) <= REL_RMS_TOL
+    # also elementwise: nothing may be off by more than a few bf16 roundings of the row/column scale
+    assert float((got[:M] - ref[:M]).abs().max()) <= 0.05 * float(ref[:M].abs().max()) + 1e-6
+
+
+def test_gemm_alpha_fp16_fp32_outputs(ckb, oracle, variant):
+    M, N, K = 128, 256, 512
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=5)
+    alpha = torch.tensor(0.37, dtype=torch.float32).cuda()
+    ref = oracle.scaled_mm_nvfp4(to_bits(qx), to_bits(qw), 0.0, 0.0, to_bits(sfx), to_bits(sfw), alpha=0.37, out_dtype=0)
+    ref = torch.from_numpy(ref)
+    for dt in (torch.float16, torch.float32, torch.bfloat16):
+        y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, out_dtype=dt, alpha=alpha)
+        assert y.dtype == dt
+        assert rel_rms(y.cpu().float(), ref) <= REL_RMS_TOL
+    y0 = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)       # default out dtype
+    assert y0.dtype == torch.bfloat16
+
+
+def test_gemm_first_config_golden(ckb, golden_large, oracle, variant):
+    import hashlib
+    rng = np.random.default_rng(0)
+    x32 = rng.standard_normal((256, 1024), dtype=np.float32)
+    w32 = (rng.standard_normal((1024, 1024), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    xb, wb = oracle.narrow(x32, 2), oracle.narrow(w32, 2)
+    if hashlib.sha256(xb.tobytes()).hexdigest() != golden_large["x_bits_sha256"]:
+        pytest.skip("numpy generator stream differs")
+    tsx = torch.tensor(golden_large["ts_x"], dtype=torch.float32).cuda()
+    tsw = torch.tensor(golden_large["ts_w"], dtype=torch.float32).cuda()
+    qx, sfx = ckb.quantize_nvfp4(from_bits(xb, 2).cuda(), tsx)
+    qw, sfw = ckb.quantize_nvfp4(from_bits(wb, 2).cuda(), tsw)
+    assert hashlib.sha256(to_bits(qw).tobytes()).hexdigest() == golden_large["qw_sha256"]
+    y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+    ref = from_bits(np.array(golden_large["y_sample_bits"], np.uint16), 2).float()
+    assert rel_rms(y.cpu().float()[::8, ::8], ref) <= REL_RMS_TOL
+    assert abs(float(y.float().pow(2).mean().sqrt()) - golden_large["y_rms"]) < 1e-2 * golden_large["y_rms"]
+
+
+FLUX = [(4608, 9216, 3072), (4608, 3072, 3072), (4608, 12288, 3072), (4608, 3072, 12288)]
+WAN_T5 = [(32760, 5120, 5120), (32760, 13824, 5120), (512, 10240, 4096), (64, 4096, 10240), (16, 10240, 4096)]
+
+
+@pytest.mark.parametrize("mnk", FLUX + WAN_T5, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_full_size_vs_cublaslt(mnk, ckb, variant):
+    """BASELINE-sized linears: same quantized operands through torch's cuBLASLt NVFP4 matmul (the kernel behind the
+    reference eager backend) and through ours; plus linearity in alpha, which needs no reference at all."""
+    M, N, K = mnk
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=K + N, outliers=True)
+    y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+    assert torch.isfinite(y.float()).all()
+    try:
+        ref = torch_scaled_mm(qx, sfx, tsx, qw, sfw, tsw)
+    except Exception as e:   # pragma: no cover - depends on the torch / cuBLASLt build on the box
+        pytest.skip(f"torch scaled_mm NVFP4 unavailable here: {type(e).__name__}: {e}")
+    Mr = min(M, ref.shape[0])
+    assert rel_rms(y[:Mr].float(), ref[:Mr].float()) <= REL_RMS_TOL
+    # quantization error against the unquantized bf16 linear stays at the format's level (~0.13 RMS on these inputs)
+    hp = (x[:1024].float() @ w.float().t())
+    assert rel_rms(y[:1024].float(), hp) < 0.25
+    # linearity: alpha = 2 * tsx * tsw doubles the output exactly (power-of-two scaling commutes with rounding)
+    y2 = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, alpha=(2.0 * tsx * tsw))
+    assert torch.equal(y2.float(), 2.0 * y.float())
+
+
+def test_gemm_rejects_bad_arguments(ckb):
+    qx = torch.zeros((128, 64), dtype=torch.uint8, device="cuda")
+    qw = torch.zeros((64, 64), dtype=torch.uint8, device="cuda")
+    ts = torch.tensor(1.0, device="cuda")
+    sfa = torch.zeros((128, 8), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    sfb = torch.zeros((128, 8), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    with pytest.raises(AssertionError):
+        ckb.scaled_mm_nvfp4(qx, qw[:, :32].contiguous(), ts, ts, sfa, sfb)     # K mismatch
+    with pytest.raises(AssertionError):
+        ckb.scaled_mm_nvfp4(qx, qw, ts, ts, sfa[:64], sfb)                      # wrong scale shape
+    from comfy_kitchen_b200 import _lib
+    L = _lib.load()
+    rc = L.ck_b200_scaled_mm_nvfp4(qx.data_ptr(), sfa.data_ptr(), qw.data_ptr(), sfb.data_ptr(), ts.data_ptr(),
+                                   ts.data_ptr(), None, None, 2, qx.data_ptr(), 2, 128, 60, 128, None, 0, None)
+    assert rc == 1 and "multiple of 8" in _lib.last_error()
+
+
+def test_zero_sized(ckb):
+    ts = torch.tensor(1.0, device="cuda")
+    q, sf = ckb.quantize_nvfp4(torch.empty((0, 64), dtype=torch.bfloat16, device="cuda"), ts)
+    assert tuple(q.shape) == (0, 32) and tuple(sf.shape) == (0, 4)
