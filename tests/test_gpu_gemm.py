@@ -102,8 +102,9 @@ def test_gemm_vs_oracle(mnk, with_bias, ckb, oracle, variant):
 def test_gemm_alpha_fp16_fp32_outputs(ckb, oracle, variant):
     M, N, K = 128, 256, 512
     x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=5)
-    alpha = torch.tensor(0.37, dtype=torch.float32).cuda()
-    ref = oracle.scaled_mm_nvfp4(to_bits(qx), to_bits(qw), 0.0, 0.0, to_bits(sfx), to_bits(sfw), alpha=0.37, out_dtype=0)
+    a = float(np.float32(0.37) * np.float32(float(tsx)) * np.float32(float(tsw)))
+    alpha = torch.tensor(a, dtype=torch.float32).cuda()
+    ref = oracle.scaled_mm_nvfp4(to_bits(qx), to_bits(qw), 0.0, 0.0, to_bits(sfx), to_bits(sfw), alpha=a, out_dtype=0)
     ref = torch.from_numpy(ref)
     for dt in (torch.float16, torch.float32, torch.bfloat16):
         y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, out_dtype=dt, alpha=alpha)
