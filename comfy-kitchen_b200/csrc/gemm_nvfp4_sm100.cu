@@ -488,7 +488,7 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     g.k_iters = (int)ceil_div64(K, 256);
     g.m_tiles = g.n_tiles = 0;
     int variant = g_gemm_variant.load();
-    if (variant == 0) variant = 1;
+    if (variant == 0) variant = (N > 128) ? 2 : 1;   // 128x256 tiles halve the operand traffic per flop
     cudaStream_t s = (cudaStream_t)stream;
     if (variant == 2) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s);
     return launch_gemm<128>(a_dev, b_dev, g, K, sms, s);
