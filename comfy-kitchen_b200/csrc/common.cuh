@@ -22,6 +22,7 @@ extern std::atomic<long long> g_launches;
 // Tuning switches (ck_b200_set_tuning).
 extern std::atomic<int> g_quant_variant;
 extern std::atomic<int> g_gemm_variant;
+extern std::atomic<int> g_gemm_debug;
 
 // Checks that the current device is compute capability 10.x (cached per device ordinal).
 int check_device(int* sm_count_out);

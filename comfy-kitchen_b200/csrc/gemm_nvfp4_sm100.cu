@@ -3,14 +3,21 @@
 //   out[M,N] = out_dtype( alpha * sum_k e2m1(a[m,k]) e4m3(sfa[m,k/16]) e2m1(b[n,k]) e4m3(sfb[n,k/16]) + bias[n] )
 //
 // Structure (one persistent CTA per SM, 6 warps, no cluster, no multicast):
-//   warp 0   producer: one lane issues TMA tile loads of packed A/B (128-byte swizzle) and plain bulk
-//            copies of the scale-factor chunks into a ring of shared-memory stages (mbarrier complete_tx).
-//   warp 1   MMA issuer: one lane copies the stage's scale factors shared -> tensor memory (tcgen05.cp),
-//            issues tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BN x 64 per instruction, fp32
-//            accumulators in tensor memory) and commits stage release / accumulator-ready barriers.
-//   warps 2-5 epilogue: tcgen05.ld of the accumulator quadrant that the warp may access, alpha and bias,
-//            conversion to the output dtype, 16-byte global stores.  With BN = 128 two accumulator
-//            buffers let the epilogue of tile i overlap the main loop of tile i+1.
+//   warp 0   producer: TMA tile loads of packed A/B (128-byte swizzle) and plain bulk copies of the
+//            scale-factor chunks into a ring of shared-memory stages (mbarrier complete_tx).
+//   warp 1   MMA issuer: copies the stage's scale factors shared -> tensor memory (tcgen05.cp), issues
+//            tcgen05.mma.kind::mxf4nvf4.block_scale (128 x BN x 64 per instruction, fp32 accumulators in
+//            tensor memory) and commits stage-release / accumulator-ready barriers.
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator quadrant the warp may access, alpha and bias,
+//            conversion, then either a swizzled shared-memory staging tile written out with a TMA store
+//            (16-bit outputs: full 64-byte row segments) or direct 16-byte stores (fp32 output).
+// Warps 0 and 1 run their loops with all lanes (uniform control flow keeps descriptor and address arithmetic
+// on the uniform datapath) and predicate only the issuing instructions on one elected lane.
+//
+// Tensor memory (512 columns) holds two accumulators so the epilogue of tile i overlaps the main loop of
+// tile i+1.  With BN = 128 they are disjoint.  With BN = 256 two full accumulators plus the scale factors
+// do not fit, so the accumulators overlap in 64 columns ([0,256) and [192,448)): the epilogue drains the
+// shared columns first and releases them through their own barrier, after which the next tile's MMAs may start.
 //
 // The scale tensors are in the 128x4 tiled layout of cuBLAS (comfy_kitchen/float_utils.py:292-326): the
 // scales of 128 rows x 64 K-elements are one contiguous 512-byte chunk shaped 32 x 16 bytes, which is
@@ -36,9 +43,11 @@ constexpr int BK_BYTES = 128;       // packed bytes of K per stage = 256 element
 constexpr int CHUNKS = 4;           // 64-element MMA steps per stage
 constexpr int SF_CHUNK_BYTES = 512; // scales of 128 rows x 64 elements
 constexpr int NUM_THREADS = 192;
+constexpr int EPI_COLS = 32;        // accumulator columns per epilogue step
+constexpr int STAGING_BYTES_PER_WARP = 32 * EPI_COLS * 2;   // 32 rows x 32 sixteen-bit outputs
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // about 1.5 s
 
-enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4 };
+enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5 };
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -54,25 +63,32 @@ struct GemmArgs {
     int sfb_bands;        // 128-row bands in the B scale tensor
     int k_iters;          // ceil(K / 256)
     int m_tiles, n_tiles;
+    int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
+    int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
 };
 
 template <int BN>
 struct Cfg {
     static constexpr int kStages = (BN == 128) ? 6 : 4;
-    static constexpr int kAccStages = (BN == 128) ? 2 : 1;
     static constexpr int kBands = BN / 128;                       // 128-row bands of B per tile
     static constexpr int kABytes = BM * BK_BYTES;                 // 16 KiB
     static constexpr int kBBytes = BN * BK_BYTES;
     static constexpr int kSfaBytes = CHUNKS * SF_CHUNK_BYTES;     // 2 KiB
     static constexpr int kSfbBytes = kBands * CHUNKS * SF_CHUNK_BYTES;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    // tensor-memory columns: accumulators, then two alternating scale-factor regions
-    static constexpr int kSfaCols = CHUNKS * 4;
-    static constexpr int kSfbCols = CHUNKS * 4 * kBands;
-    static constexpr int kSfCol0 = kAccStages * BN;
+    static constexpr int kStagingBytes = 4 * STAGING_BYTES_PER_WARP;   // 8 KiB, one tile per epilogue warp
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + kBarrierBytes;
+    // tensor-memory columns: two accumulators (overlapping by kOverlapCols when BN = 256), then two alternating
+    // scale-factor regions, each holding the scales of two 64-element steps
+    static constexpr int kOverlapCols = (BN == 256) ? 64 : 0;
+    static constexpr int kAcc1Col = BN - kOverlapCols;
+    static constexpr int kSfCol0 = kAcc1Col + BN;
+    static constexpr int kSfaColsHalf = 2 * 4;
+    static constexpr int kSfbColsHalf = 2 * 4 * kBands;
+    static constexpr int kSfRegionCols = kSfaColsHalf + kSfbColsHalf;
     static constexpr int kTmemCols = 512;
-    static_assert(kSfCol0 + 2 * (kSfaCols + kSfbCols) <= kTmemCols, "tensor memory budget");
+    static_assert(kSfCol0 + 2 * kSfRegionCols <= kTmemCols, "tensor memory budget");
     static_assert(kSmemBytes <= 232448, "shared memory budget");
     // instruction descriptor of tcgen05.mma.kind::mxf4nvf4.block_scale: A,B = packed e2m1 (format 1), K-major,
     // UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
@@ -120,6 +136,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
+                 "r"(y), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest N store groups have finished reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy shared-memory writes visible to the async proxy (TMA store reads)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
@@ -153,15 +183,29 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// One lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
 
-// Shared-memory matrix descriptor (sm_100 version 1).  Addresses and offsets are in 16-byte units.
+// Shared-memory matrix descriptor (sm_100 version 1), split in two 32-bit halves so that the issuing warp only
+// adds to the low half.  Addresses and offsets are in 16-byte units.
+//   low  = (address >> 4) | (leading byte offset >> 4) << 16
+//   high = (stride byte offset >> 4) | version 1 << 14 | layout << 29
 //   operands: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
 //   scale chunks: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-    return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
-           (1ull << 46) | ((uint64_t)layout << 61);
-}
 constexpr uint32_t LAYOUT_SWIZZLE_NONE = 0, LAYOUT_SWIZZLE_128B = 2;
+constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout) { return (sbo_bytes >> 4) | (1u << 14) | (layout << 29); }
+constexpr uint32_t kOperandDescHi = desc_hi(1024, LAYOUT_SWIZZLE_128B);
+constexpr uint32_t kOperandDescLoFlags = (16u >> 4) << 16;
+constexpr uint32_t kSfDescHi = desc_hi(128, LAYOUT_SWIZZLE_NONE);
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
 
 // ---- epilogue helpers -----------------------------------------------------------------------------
 
@@ -171,11 +215,9 @@ __device__ __forceinline__ float bias_at(const void* bias, int dtype, int n) {
     return ((const float*)bias)[n];
 }
 
-// Store 32 consecutive outputs of one row starting at column n0 (n0 % 32 == 0); N % 8 == 0 so groups of
-// 8 columns are either fully inside or fully outside.
-__device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int n0, const uint32_t (&acc)[32],
-                                            float alpha) {
-    float y[32];
+// alpha * acc (+ bias) for 32 consecutive columns starting at n0
+__device__ __forceinline__ void scale_row32(const GemmArgs& g, int n0, const uint32_t (&acc)[32], float alpha,
+                                            float (&y)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(acc[i]) * alpha;
     if (g.bias) {
@@ -183,6 +225,20 @@ __device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int 
         for (int i = 0; i < 32; ++i)
             if (n0 + i < g.N) y[i] += bias_at(g.bias, g.bias_dtype, n0 + i);
     }
+}
+
+__device__ __forceinline__ uint32_t pack16(float a, float b, int out_dtype) {
+    if (out_dtype == CK_B200_DTYPE_BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Direct global stores of 32 consecutive outputs of one row (n0 % 32 == 0; N % 8 == 0 so groups of 8 columns are
+// either fully inside or fully outside).
+__device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int n0, const float (&y)[32]) {
     if (g.out_dtype == CK_B200_DTYPE_F32) {
         float* p = (float*)g.out + row * g.N + n0;
 #pragma unroll
@@ -197,15 +253,7 @@ __device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int 
             uint4 o;
             uint32_t* w = &o.x;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (g.out_dtype == CK_B200_DTYPE_BF16) {
-                    __nv_bfloat162 v = __floats2bfloat162_rn(y[8 * j + 2 * i], y[8 * j + 2 * i + 1]);
-                    w[i] = *reinterpret_cast<uint32_t*>(&v);
-                } else {
-                    __half2 v = __floats2half2_rn(y[8 * j + 2 * i], y[8 * j + 2 * i + 1]);
-                    w[i] = *reinterpret_cast<uint32_t*>(&v);
-                }
-            }
+            for (int i = 0; i < 4; ++i) w[i] = pack16(y[8 * j + 2 * i], y[8 * j + 2 * i + 1], g.out_dtype);
             *reinterpret_cast<uint4*>(p + 8 * j) = o;
         }
     }
@@ -213,20 +261,22 @@ __device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int 
 
 // ---- kernel -----------------------------------------------------------------------------------------
 
-template <int BN>
+template <int BN, bool DBG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const GemmArgs g) {
+                  const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    uint8_t* staging = smem + C::kStages * C::kStageBytes;      // 4 x 2 KiB, 64-byte swizzled rows
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::kStagingBytes);
     uint64_t* full_bar = bars;                                  // [kStages]  producer -> MMA
     uint64_t* empty_bar = bars + C::kStages;                    // [kStages]  MMA -> producer
-    uint64_t* acc_full_bar = bars + 2 * C::kStages;             // [kAccStages] MMA -> epilogue
-    uint64_t* acc_empty_bar = acc_full_bar + C::kAccStages;     // [kAccStages] epilogue -> MMA
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + C::kAccStages);
+    uint64_t* acc_full_bar = bars + 2 * C::kStages;             // [2] MMA -> epilogue
+    uint64_t* acc_empty_bar = acc_full_bar + 2;                 // [2] epilogue -> MMA: accumulator drained
+    uint64_t* overlap_bar = acc_empty_bar + 2;                  // [1] epilogue -> MMA: shared columns drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(overlap_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -237,10 +287,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        for (int s = 0; s < C::kAccStages; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&acc_full_bar[s]), 1);
             mbar_init(smem_u32(&acc_empty_bar[s]), 128);
         }
+        mbar_init(smem_u32(overlap_bar), 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -256,119 +307,201 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_tiles = g.m_tiles * g.n_tiles;
+    // cycle counters of the debug build (DBG): compiled out otherwise
+    auto now = [] { return DBG ? clock64() : 0ll; };
 
     if (warp == 0) {
         // ---------------- producer ----------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int tm = tile % g.m_tiles, tn = tile / g.m_tiles;
-                for (int kb = 0; kb < g.k_iters; ++kb) {
-                    ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
-                    if (!ok) break;
-                    uint8_t* st = smem + stage * C::kStageBytes;
-                    const uint32_t bar = smem_u32(&full_bar[stage]);
-                    const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
-                    int sfb_present = 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        long long waited = 0;
+        const long long t_begin = now();
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int tm = tile % g.m_tiles, tn = tile / g.m_tiles;
+            int sfb_present = 0;
+#pragma unroll
+            for (int b = 0; b < C::kBands; ++b)
+                if (tn * C::kBands + b < g.sfb_bands) ++sfb_present;
+            const uint8_t* sfa_src = g.sfa + (int64_t)tm * g.sf_cbg * SF_CHUNK_BYTES;
+            const uint8_t* sfb_src = g.sfb + (int64_t)tn * C::kBands * g.sf_cbg * SF_CHUNK_BYTES;
+            for (int kb = 0; kb < g.k_iters; ++kb) {
+                const long long t0 = now();
+                ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                waited += now() - t0;
+                if (!ok) break;
+                const uint32_t st = smem_u32(smem) + stage * C::kStageBytes;
+                const uint32_t bar = smem_u32(&full_bar[0]) + stage * 8;
+                const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                const uint32_t sf_bytes = nchunk * SF_CHUNK_BYTES;
+                if (elect_one()) {
+                    mbar_expect_tx(bar, C::kABytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
+                    tma_load_2d(st, &tmap_a, kb * BK_BYTES, tm * BM, bar);
+                    tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * BN, bar);
+                    bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)kb * CHUNKS * SF_CHUNK_BYTES, sf_bytes, bar);
 #pragma unroll
                     for (int b = 0; b < C::kBands; ++b)
-                        if (tn * C::kBands + b < g.sfb_bands) ++sfb_present;
-                    mbar_expect_tx(bar, C::kABytes + C::kBBytes + (1 + sfb_present) * nchunk * SF_CHUNK_BYTES);
-                    tma_load_2d(smem_u32(st), &tmap_a, kb * BK_BYTES, tm * BM, bar);
-                    tma_load_2d(smem_u32(st + C::kABytes), &tmap_b, kb * BK_BYTES, tn * BN, bar);
-                    bulk_load(smem_u32(st + C::kABytes + C::kBBytes),
-                              g.sfa + ((int64_t)tm * g.sf_cbg + kb * CHUNKS) * SF_CHUNK_BYTES, nchunk * SF_CHUNK_BYTES, bar);
-#pragma unroll
-                    for (int b = 0; b < C::kBands; ++b) {
-                        const int band = tn * C::kBands + b;
-                        if (band < g.sfb_bands)
-                            bulk_load(smem_u32(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes),
-                                      g.sfb + ((int64_t)band * g.sf_cbg + kb * CHUNKS) * SF_CHUNK_BYTES,
-                                      nchunk * SF_CHUNK_BYTES, bar);
-                    }
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+                        if (b < sfb_present)
+                            bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes,
+                                      sfb_src + ((int64_t)b * g.sf_cbg + kb * CHUNKS) * SF_CHUNK_BYTES, sf_bytes, bar);
                 }
+                __syncwarp();
+                if (++stage == C::kStages) { stage = 0; phase ^= 1; }
             }
         }
+        if (DBG && blockIdx.x == 0 && lane == 0)
+            printf("[gemm bn%d cta0] producer: total %lld cycles, waiting for free stages %lld\n", BN, now() - t_begin,
+                   waited);
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            int stage = 0, acc = 0, sfbuf = 0;
-            uint32_t phase = 0, acc_phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                ok = mbar_wait(smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1, abort_flag, WAIT_ACC_EMPTY);
+        int stage = 0, acc = 0, local_tile = 0;
+        uint32_t phase = 0, acc_phase = 0;
+        bool ok = true;
+        long long wait_acc = 0, wait_full = 0;
+        const long long t_begin = now();
+        const uint32_t smem_enc = smem_u32(smem) >> 4;   // descriptor addresses are in 16-byte units
+        const uint32_t sf_t0 = tmem_base + C::kSfCol0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+            long long t0 = now();
+            // the accumulator's own columns: drained by the epilogue two tiles ago
+            ok = mbar_wait(smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1, abort_flag, WAIT_ACC_EMPTY);
+            // the columns shared with the other accumulator: drained first by the previous tile's epilogue
+            if (C::kOverlapCols > 0 && local_tile > 0 && ok)
+                ok = mbar_wait(smem_u32(overlap_bar), (uint32_t)(local_tile - 1) & 1u, abort_flag, WAIT_OVERLAP);
+            ok = __all_sync(0xffffffffu, ok);
+            wait_acc += now() - t0;
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * C::kAcc1Col;
+            for (int kb = 0; kb < g.k_iters; ++kb) {
+                t0 = now();
+                ok = mbar_wait(smem_u32(&full_bar[0]) + stage * 8, phase, abort_flag, WAIT_STAGE_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                wait_full += now() - t0;
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < g.k_iters; ++kb) {
-                    ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, WAIT_STAGE_FULL);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t st = smem_u32(smem + stage * C::kStageBytes);
-                    const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
-                    const uint32_t sfa_t = tmem_base + C::kSfCol0 + sfbuf * (C::kSfaCols + C::kSfbCols);
-                    const uint32_t sfb_t = sfa_t + C::kSfaCols;
-                    for (int j = 0; j < nchunk; ++j) {
-                        tc_cp_sf(sfa_t + 4 * j,
-                                 smem_desc(st + C::kABytes + C::kBBytes + j * SF_CHUNK_BYTES, 0, 128, LAYOUT_SWIZZLE_NONE));
+                const uint32_t st_enc = smem_enc + stage * (C::kStageBytes >> 4);
+                const uint32_t a_lo = st_enc | kOperandDescLoFlags;
+                const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+                const uint32_t sfa_lo = st_enc + ((C::kABytes + C::kBBytes) >> 4);
+                const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+                const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                if (elect_one()) {
+                    // scale factors of step j go to region j/2 (the two regions alternate, so a copy never
+                    // overwrites scales that the MMAs issued just before it still read)
 #pragma unroll
-                        for (int b = 0; b < C::kBands; ++b)
-                            tc_cp_sf(sfb_t + 4 * C::kBands * j + 4 * b,
-                                     smem_desc(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes +
-                                                   j * SF_CHUNK_BYTES,
-                                               0, 128, LAYOUT_SWIZZLE_NONE));
+                    for (int j = 0; j < CHUNKS; ++j) {
+                        if (j < nchunk) {
+                            const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
+                            const uint32_t sfb_t =
+                                sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
+                            tc_cp_sf(sfa_t, desc64(sfa_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
+#pragma unroll
+                            for (int b = 0; b < C::kBands; ++b)
+                                tc_cp_sf(sfb_t + 4 * b,
+                                         desc64(sfb_lo + (b * C::kSfaBytes + j * SF_CHUNK_BYTES) / 16, kSfDescHi));
+                        }
                     }
-                    const uint64_t adesc = smem_desc(st, 16, 1024, LAYOUT_SWIZZLE_128B);
-                    const uint64_t bdesc = smem_desc(st + C::kABytes, 16, 1024, LAYOUT_SWIZZLE_128B);
-                    for (int j = 0; j < nchunk; ++j) {
-                        // 64 elements of K = 32 bytes = 2 descriptor address units inside the swizzle row
-                        tc_mma(d_tmem, adesc + 2 * j, bdesc + 2 * j, C::kIdesc, sfa_t + 4 * j,
-                               sfb_t + 4 * C::kBands * j, (kb | j) ? 1u : 0u);
+#pragma unroll
+                    for (int j = 0; j < CHUNKS; ++j) {
+                        if (j < nchunk) {
+                            const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
+                            const uint32_t sfb_t =
+                                sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
+                            // 64 elements of K = 32 bytes = 2 descriptor address units inside the swizzle row
+                            tc_mma(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
+                                   C::kIdesc, sfa_t, sfb_t, (j != 0 || kb != 0) ? 1u : 0u);
+                        }
                     }
-                    tc_commit(smem_u32(&empty_bar[stage]));   // stage reusable once these MMAs have read it
-                    sfbuf ^= 1;
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+                    tc_commit(smem_u32(&empty_bar[0]) + stage * 8);   // stage reusable once these MMAs have read it
                 }
-                if (!ok) break;
-                tc_commit(smem_u32(&acc_full_bar[acc]));      // accumulator complete
-                if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+                __syncwarp();
+                if (++stage == C::kStages) { stage = 0; phase ^= 1; }
             }
+            if (!ok) break;
+            if (elect_one()) tc_commit(smem_u32(&acc_full_bar[acc]));   // accumulator complete
+            __syncwarp();
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
         }
+        if (DBG && blockIdx.x == 0 && lane == 0)
+            printf("[gemm bn%d cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", BN,
+                   now() - t_begin, wait_acc, wait_full);
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const int quad = warp & 3;   // tensor-memory lanes [32*quad, 32*quad+32) are the ones this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
-        float alpha = 0.0f;
-        bool alpha_loaded = false;
         bool ok = true;
+        long long wait_acc = 0;
+        const long long t_begin = now();
+        const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
+        uint8_t* my_staging = staging + quad * STAGING_BYTES_PER_WARP;
+        const uint32_t my_staging_u32 = smem_u32(my_staging);
+        constexpr int kSteps = BN / EPI_COLS;
+        constexpr int kOverlapSteps = C::kOverlapCols / EPI_COLS;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int tm = tile % g.m_tiles, tn = tile / g.m_tiles;
-            if (!alpha_loaded) {
-                alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
-                alpha_loaded = true;
-            }
+            const long long tw = now();
             ok = mbar_wait(smem_u32(&acc_full_bar[acc]), acc_phase, abort_flag, WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
+            wait_acc += now() - tw;
             if (!ok) break;
             tc_fence_after();
-            const int64_t row = (int64_t)tm * BM + quad * 32 + lane;
-            const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            const int row0 = tm * BM + quad * 32;
+            const int64_t row = (int64_t)row0 + lane;
+            const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * C::kAcc1Col;
+            // accumulator 0 shares its last columns with accumulator 1's first ones: drain those first
+            const int first_step = (C::kOverlapCols > 0 && acc == 0) ? kSteps - kOverlapSteps : 0;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int i = 0; i < kSteps; ++i) {
+                const int s = (first_step + i) % kSteps;
                 uint32_t v[32];
-                tc_ld32(t0 + c, v);
+                tc_ld32(t_acc + s * EPI_COLS, v);
                 tc_wait_ld();
-                const int n0 = tn * BN + c;
-                if (row < g.M && n0 < g.N) store_row32(g, row, n0, v, alpha);
+                if (C::kOverlapCols > 0 && i == kOverlapSteps - 1) {   // shared columns are in registers now
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(overlap_bar));
+                }
+                const int n0 = tn * BN + s * EPI_COLS;
+                float y[32];
+                scale_row32(g, n0, v, alpha, y);
+                if (g.tma_store) {
+                    // 32 rows x 64 bytes, 16-byte pieces XOR-swizzled with (row/2)%4: the 64-byte swizzle of the
+                    // output tensor map, and conflict-free for these stores
+                    if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the staging tile
+                    __syncwarp();
+                    uint8_t* rowp = my_staging + lane * 64;
+                    const int sw = (lane >> 1) & 3;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        uint4 o;
+                        o.x = pack16(y[8 * p + 0], y[8 * p + 1], g.out_dtype);
+                        o.y = pack16(y[8 * p + 2], y[8 * p + 3], g.out_dtype);
+                        o.z = pack16(y[8 * p + 4], y[8 * p + 5], g.out_dtype);
+                        o.w = pack16(y[8 * p + 6], y[8 * p + 7], g.out_dtype);
+                        *reinterpret_cast<uint4*>(rowp + ((p ^ sw) << 4)) = o;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && n0 < g.N && row0 < g.M) {   // the store clips rows >= M and columns >= N itself
+                        tma_store_2d(&tmap_out, n0, row0, my_staging_u32);
+                        tma_store_commit();
+                    }
+                } else if (row < g.M && n0 < g.N) {
+                    store_row32(g, row, n0, y);
+                }
             }
             tc_fence_before();
             mbar_arrive(smem_u32(&acc_empty_bar[acc]));
-            if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
         }
+        if (g.tma_store && lane == 0) tma_store_wait_all();   // global writes complete before the CTA exits
+        if (DBG && blockIdx.x == 0 && threadIdx.x == 64)
+            printf("[gemm bn%d cta0] epilogue: total %lld cycles, waiting for accumulators %lld\n", BN, now() - t_begin,
+                   wait_acc);
     }
 
     tc_fence_before();
@@ -410,29 +543,49 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    if (r != CUDA_SUCCESS)
+        return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled (operand) failed with CUresult %d", (int)r);
+    return CK_B200_OK;
+}
+
+// 16-bit output [M, N] row-major, boxes of 32 columns (64 bytes) x 32 rows, 64-byte swizzle.
+int make_output_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    cuuint32_t box[2] = {(cuuint32_t)EPI_COLS, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
     return CK_B200_OK;
 }
 
 template <int BN>
 int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream) {
     using C = Cfg<BN>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
+    auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true> : gemm_nvfp4_kernel<BN, false>;
     // opting in to large dynamic shared memory is per function and per device; doing it on every call is cheap
-    attr_err = cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    (void)once;
+    cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (attr_err != cudaSuccess)
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
                     cudaGetErrorString(attr_err));
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, mo;
     if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM)) return rc;
     if (int rc = make_operand_map(&mb, b, g.N, K / 2, BN)) return rc;
+    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
+    if (g.tma_store) {
+        if (int rc = make_output_map(&mo, g.out, g.M, g.N)) return rc;
+    } else {
+        mo = ma;   // not used by the kernel
+    }
     g.m_tiles = (int)ceil_div64(g.M, BM);
     g.n_tiles = (int)ceil_div64(g.N, BN);
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    gemm_nvfp4_kernel<BN><<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mb, g);
+    kernel<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(cudaGetLastError());
     return CK_B200_OK;
@@ -487,6 +640,8 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     g.sfb_bands = (int)ceil_div64(N, 128);
     g.k_iters = (int)ceil_div64(K, 256);
     g.m_tiles = g.n_tiles = 0;
+    g.tma_store = 0;
+    g.debug = g_gemm_debug.load();
     int variant = g_gemm_variant.load();
     if (variant == 0) variant = (N > 128) ? 2 : 1;   // 128x256 tiles halve the operand traffic per flop
     cudaStream_t s = (cudaStream_t)stream;

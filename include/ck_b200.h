@@ -113,6 +113,7 @@ int ck_b200_read_device_status(int* status_out);
  * environment switches, comfy_kitchen/backends/cuda/__init__.py:212-215, do not touch this path). */
 #define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions everywhere, 1 = shared-reciprocal exact division (default) */
 #define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic */
+#define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the GEMM kernel's first CTA prints the cycles its roles spent waiting */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus
