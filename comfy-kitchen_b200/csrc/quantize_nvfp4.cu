@@ -21,7 +21,6 @@
 namespace ckb {
 namespace {
 
-constexpr int kUnitsPerWarp = 4;   // consecutive 64-column groups a warp has in flight
 constexpr int kWarpsPerBlock = 8;
 
 // ---- conversions ------------------------------------------------------------------------------
@@ -135,18 +134,81 @@ struct Input<CK_B200_DTYPE_F32> {
     }
 };
 
-// ---- exact division by a shared divisor ----------------------------------------------------------
+// ---- exact arithmetic helpers ---------------------------------------------------------------------
 
-// Correctly rounded x / t from r = RN(1/t): two rounds of residual correction (Markstein).  The first
-// round turns the two-ulp estimate x*r into a faithful quotient, the second makes it the correctly
-// rounded one.  Valid while no intermediate leaves the normal range: the caller checks
-// 2^-64 <= t <= 2^64 and |x| <= 2^20 * t and otherwise takes the IEEE division.  The sign of the
-// result is forced to the sign of x so that -0 (and negative values that round to zero) stay negative.
-__device__ __forceinline__ float div_shared(float x, float t, float r) {
-    float q = __fmul_rn(x, r);
-    q = fmaf(fmaf(-t, q, x), r, q);
-    q = fmaf(fmaf(-t, q, x), r, q);
-    return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+// Correctly rounded a / b from rb = RN(1/b): two rounds of residual correction (Markstein).  The first round
+// turns the two-ulp estimate a*rb into a faithful quotient, the second makes it the correctly rounded one.
+// Valid while no intermediate leaves the normal range (the callers check the operand ranges).
+__device__ __forceinline__ float div_by_reciprocal(float a, float b, float rb) {
+    float q = __fmul_rn(a, rb);
+    q = fmaf(fmaf(-b, q, a), rb, q);
+    q = fmaf(fmaf(-b, q, a), rb, q);
+    return q;
+}
+
+__device__ __forceinline__ float rcp_approx(float v) {   // one MUFU instruction, at most 1 ulp off for normal v
+    float r;
+    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+// Block scale byte and decode scale t = ts * float(byte) for a block whose amax is given
+// (eager/quantization.py:142-146): e4m3( min(amax / 6 / ts, 448) ).  `fast`: amax and ts are inside
+// [2^-60, 2^60], where the reciprocal-based divisions below are exact; otherwise IEEE divisions.
+__device__ __forceinline__ void block_scale(float amax, float ts, float rcp_ts, bool fast, uint32_t& s8, float& t) {
+    float sbs;
+    if (fast) {
+        const float bs = div_by_reciprocal(amax, 6.0f, 0x1.555556p-3f);   // RN(1/6)
+        sbs = div_by_reciprocal(bs, ts, rcp_ts);
+    } else {
+        sbs = __fdiv_rn(__fdiv_rn(amax, 6.0f), ts);
+    }
+    sbs = fminf(sbs, 448.0f);
+    s8 = f32_to_e4m3_rne(sbs);
+    t = __fmul_rn(ts, e4m3_to_f32((uint8_t)s8));
+}
+
+// Eight elements -> packed e2m1 word (element 2i in the high nibble), exactly as RNE(e2m1)(RN(x / t)), by IEEE
+// division.  Zero decode scale: every element encodes +0 (eager/quantization.py:149-153).
+__device__ __forceinline__ uint32_t quantize8_exact(const float (&f)[8], float t) {
+    if (t == 0.0f) return 0u;
+    float d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d[i] = __fdiv_rn(f[i], t);
+    return pack8_e2m1_hi_first(d);   // satfinite clamps to +-6 like the reference's clamp before rounding
+}
+
+// The same word for a decode scale in [2^-100, 2^100] without the IEEE division routine: r = RN(1/t), then each
+// quotient by two rounds of residual correction.  The sign of x is forced onto the result so that -0 and negative
+// values that round to zero keep their sign bit.
+__device__ __forceinline__ uint32_t quantize8_reciprocal(const float (&f)[8], float t) {
+    const float r = __frcp_rn(t);
+    float d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float q = div_by_reciprocal(f[i], t, r);
+        d[i] = __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(f[i]) & 0x80000000u));
+    }
+    return pack8_e2m1_hi_first(d);
+}
+
+// The same word from a bracket instead of a division.  With r within 1 ulp of 1/t, x*(r - 8ulp) and x*(r + 8ulp)
+// (round-to-nearest products) lie below and above x/t in magnitude with the sign of x, so RN(x/t) lies between
+// them; conversion to e2m1 is monotone, hence equal codes for the two bounds are the code of RN(x/t).  The
+// bounds are 17 ulp apart, so they disagree only for quotients within 2^-19 of a rounding boundary; the caller
+// then falls back to quantize8_exact.  Needs t and r in the normal range: the caller passes r = 0 (which makes
+// the two words differ or the flag below fire) unless t is in [2^-100, 2^100].
+__device__ __forceinline__ bool quantize8_bracket(const float (&f)[8], float r, uint32_t& word) {
+    const float r_lo = __uint_as_float(__float_as_uint(r) - 8u);
+    const float r_hi = __uint_as_float(__float_as_uint(r) + 8u);
+    float d[8], e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        d[i] = __fmul_rn(f[i], r_lo);
+        e[i] = __fmul_rn(f[i], r_hi);
+    }
+    word = pack8_e2m1_hi_first(d);
+    return (word == pack8_e2m1_hi_first(e)) && (r != 0.0f);
 }
 
 // ---- quantize -------------------------------------------------------------------------------------
@@ -156,99 +218,279 @@ struct QuantArgs {
     const float* pts;
     uint8_t* q;
     uint8_t* sf;
-    int64_t rows, cols;      // logical input
-    int64_t prow, pcol;      // padded (output) shape
-    int64_t row_groups;      // roundup(prow,128)/4 : number of (band, d3) groups
-    int sf_cbg;              // scale tensor width / 4
-    int tasks_per_group;     // ceil(sf_cbg / kUnitsPerWarp)
+    int rows, cols;          // logical input
+    int prow, pcol;          // padded (output) shape
+    int row_groups;          // roundup(prow,128)/4 : number of (band, d3) groups
+    int sf_cbg;              // scale tensor width / 4 = units per row
+    int seg_units;           // units per warp (even); a row is cut into `segments` such pieces
+    int segments;
     int hi_first;
 };
 
-template <int DT, bool VEC, int VARIANT>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) quantize_nvfp4_kernel(const QuantArgs a) {
+constexpr int kRing = 6;   // units a thread keeps in flight (16-byte loads), processed two at a time
+
+// State of one lane for one segment walk.
+struct LaneCtx {
+    const char* x_row;   // first element of this lane's row
+    uint8_t* q_row;      // first packed byte of this lane's output row
+    uint8_t* sf_row;     // this lane's row inside scale chunk 0 of the band (chunks are 512 bytes apart)
+    float ts, rcp_ts;
+    bool ts_in_range, row_in, row_out, odd, hi_first;
+    int sub, cols, pcol;
+};
+
+// One pair of units (A, B) held by a warp: the two lanes that share a 16-element block split the per-block work.
+// The even lane derives scale byte, decode scale and reciprocal for the block of unit A, the odd lane for the
+// block of unit B, and they swap the results with shuffles.  `mine_in`: the block this lane derives lies inside
+// the padded output.  Returns the two packed words and leaves this lane's scale byte in s8.
+// Rare cases (operands outside the exact-reciprocal range, quotients next to a rounding boundary) are found with a
+// warp vote, so the common path has no divergent branch.
+template <int DT, int VARIANT>
+__device__ __forceinline__ void quantize_pair(const LaneCtx& c, const typename Input<DT>::Raw& raw_a,
+                                              const typename Input<DT>::Raw& raw_b, bool mine_in, uint32_t& word_a,
+                                              uint32_t& word_b, uint32_t& s8) {
     using In = Input<DT>;
-    const int lane = threadIdx.x & 31;
-    const int64_t task = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (task >= a.row_groups * a.tasks_per_group) return;
-    const int64_t group = task / a.tasks_per_group;
-    const int cbg0 = (int)(task % a.tasks_per_group) * kUnitsPerWarp;
-    const int d4 = lane >> 3, sub = lane & 7;
-    const int64_t band = group >> 5;
-    const int d3 = (int)(group & 31);
-    const int64_t r = band * 128 + d3 + 32 * d4;
-    const float ts = __ldg(a.pts);
-    const bool row_in = r < a.rows;
-
-    typename In::Raw raw[kUnitsPerWarp];
-#pragma unroll
-    for (int u = 0; u < kUnitsPerWarp; ++u) {
-        const int64_t c0 = (int64_t)(cbg0 + u) * 64 + sub * 8;
-        raw[u] = In::zero();
-        if (row_in && c0 < a.cols) {
-            if (VEC) {   // cols % 8 == 0 and 16-byte aligned base: the whole vector is inside the row
-                raw[u] = In::load_vec((const char*)a.x + (r * a.cols + c0) * In::kBytes);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (c0 + i < a.cols) In::set(raw[u], i, a.x, r * a.cols + c0 + i);
-            }
+    const bool odd = c.odd;
+    float fa[8], fb[8];
+    const float half_a = In::unpack(raw_a, fa);
+    const float half_b = In::unpack(raw_b, fb);
+    // amax of the block this lane is responsible for: its own half and the partner's half
+    const float other_half = __shfl_xor_sync(0xffffffffu, odd ? half_a : half_b, 1);
+    const float amax = fmaxf(odd ? half_b : half_a, other_half);
+    s8 = 0;
+    float t = 0.0f, rcp = 0.0f;
+    if (VARIANT == 1) {
+        const bool fast = c.ts_in_range && amax >= 0x1p-60f && amax <= 0x1p60f;
+        if (__all_sync(0xffffffffu, fast && mine_in)) {
+            block_scale(amax, c.ts, c.rcp_ts, true, s8, t);
+            rcp = rcp_approx(t);
+            // t is zero (block scale rounded to zero) or, never with these ranges, outside [2^-100, 2^100]: flag it
+            if (!(t >= 0x1p-100f && t <= 0x1p100f)) rcp = 0.0f;
+        } else if (mine_in) {
+            block_scale(amax, c.ts, c.rcp_ts, fast, s8, t);
+            if (t >= 0x1p-100f && t <= 0x1p100f) rcp = rcp_approx(t);
         }
+    } else if (mine_in) {
+        block_scale(amax, c.ts, 0.0f, false, s8, t);
     }
-
-#pragma unroll
-    for (int u = 0; u < kUnitsPerWarp; ++u) {
-        const int cbg = cbg0 + u;
-        if (cbg >= a.sf_cbg) break;   // uniform across the warp
-        const int64_t c0 = (int64_t)cbg * 64 + sub * 8;
-        float f[8];
-        float amax = In::unpack(raw[u], f);
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));   // the two halves of a 16-element block
-
-        // block scale: e4m3( min(amax / 6 / ts, 448) ), and the decode scale t = ts * float(e4m3)
-        const bool inside = (r < a.prow) && (c0 < a.pcol);
-        uint32_t s8 = 0;
-        float t = 0.0f;
-        if (inside) {
-            float sbs = __fdiv_rn(__fdiv_rn(amax, 6.0f), ts);
-            sbs = fminf(sbs, 448.0f);
-            s8 = f32_to_e4m3_rne(sbs);
-            t = __fmul_rn(ts, e4m3_to_f32((uint8_t)s8));
+    const float t_other = __shfl_xor_sync(0xffffffffu, t, 1);
+    const float t_a = odd ? t_other : t, t_b = odd ? t : t_other;
+    if (VARIANT == 1) {
+        const float rcp_other = __shfl_xor_sync(0xffffffffu, rcp, 1);
+        const float rcp_a = odd ? rcp_other : rcp, rcp_b = odd ? rcp : rcp_other;
+        const bool ok_a = quantize8_bracket(fa, rcp_a, word_a);
+        const bool ok_b = quantize8_bracket(fb, rcp_b, word_b);
+        if (__any_sync(0xffffffffu, !(ok_a && ok_b))) {
+            // next to a rounding boundary (exact ties are common when the per-tensor scale is amax/2688), or a
+            // decode scale that is zero or out of range (flagged by a zero reciprocal)
+            if (!ok_a) word_a = (rcp_a != 0.0f) ? quantize8_reciprocal(fa, t_a) : quantize8_exact(fa, t_a);
+            if (!ok_b) word_b = (rcp_b != 0.0f) ? quantize8_reciprocal(fb, t_b) : quantize8_exact(fb, t_b);
         }
-
-        uint32_t word = 0;
-        if (t != 0.0f) {   // zero decode scale: every element encodes +0 (eager/quantization.py:149-153)
-            float d[8];
-            bool fast = false;
-            if (VARIANT == 1) fast = (t >= 0x1p-64f) && (t <= 0x1p64f) && (amax <= t * 1048576.0f);
-            if (fast) {
-                const float rcp = __frcp_rn(t);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) d[i] = div_shared(f[i], t, rcp);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) d[i] = __fdiv_rn(f[i], t);
-            }
-            word = pack8_e2m1_hi_first(d);   // satfinite clamps to +-6 like the reference's clamp before rounding
-            if (!a.hi_first) word = swap_nibbles32(word);
-        }
-        if (inside) *reinterpret_cast<uint32_t*>(a.q + r * (a.pcol >> 1) + (c0 >> 1)) = word;
-
-        // gather the four block scales of this row (lanes sub = 0,2,4,6) into one 32-bit word on lane sub = 0
-        uint32_t sfw = (sub & 1) ? 0u : (s8 << (8 * (sub >> 1)));
-        sfw |= __shfl_xor_sync(0xffffffffu, sfw, 2);
-        sfw |= __shfl_xor_sync(0xffffffffu, sfw, 4);
-        if (sub == 0)
-            *reinterpret_cast<uint32_t*>(a.sf + ((band * a.sf_cbg + cbg) * 32 + d3) * 16 + d4 * 4) = sfw;
+    } else {
+        word_a = quantize8_exact(fa, t_a);
+        word_b = quantize8_exact(fb, t_b);
+    }
+    if (!c.hi_first) {
+        word_a = swap_nibbles32(word_a);
+        word_b = swap_nibbles32(word_b);
     }
 }
 
+// The four block scales of a row and unit sit on lanes of equal parity (even: unit A, odd: unit B): gather them
+// into one 32-bit word on lane sub = 0 (A) and sub = 1 (B).
+__device__ __forceinline__ uint32_t gather_scale_word(uint32_t s8, int sub) {
+    uint32_t sfw = s8 << (8 * (sub >> 1));
+    sfw |= __shfl_xor_sync(0xffffffffu, sfw, 2);
+    sfw |= __shfl_xor_sync(0xffffffffu, sfw, 4);
+    return sfw;
+}
+
+// Interior segment: every row of the warp and every column of units [u_begin, u_end) is inside the input and the
+// output and the segment holds whole pairs.  The main loop has no bounds checks: all addresses are the three
+// running pointers plus immediates, and each consumed pair of registers is refilled with the units kRing ahead.
+template <int DT, int VARIANT>
+__device__ __forceinline__ void walk_interior(const LaneCtx& c, int u_begin, int u_end) {
+    using In = Input<DT>;
+    using Raw = typename In::Raw;
+    constexpr int kUnitBytes = 64 * In::kBytes;   // input bytes of one unit in one row
+    const int sub = c.sub;
+    const char* xp = c.x_row + (u_begin * 64 + sub * 8) * In::kBytes;
+    uint8_t* qp = c.q_row + u_begin * 32 + sub * 4;
+    uint8_t* sp = c.sf_row + (u_begin + (sub & 1)) * 512;   // lane sub = 1 stores unit B's scales
+    const bool sf_lane = sub < 2;
+    int remaining = u_end - u_begin;
+
+    Raw raw[kRing];
+#pragma unroll
+    for (int k = 0; k < kRing; ++k)
+        if (k < remaining) raw[k] = In::load_vec(xp + k * kUnitBytes);
+        else raw[k] = In::zero();
+
+    auto consume = [&](int k) {
+        uint32_t wa, wb, s8;
+        quantize_pair<DT, VARIANT>(c, raw[k], raw[k + 1], true, wa, wb, s8);
+        *reinterpret_cast<uint32_t*>(qp + k * 32) = wa;
+        *reinterpret_cast<uint32_t*>(qp + k * 32 + 32) = wb;
+        const uint32_t sfw = gather_scale_word(s8, sub);
+        if (sf_lane) *reinterpret_cast<uint32_t*>(sp + k * 512) = sfw;
+    };
+
+    for (; remaining >= 2 * kRing; remaining -= kRing) {
+#pragma unroll
+        for (int k = 0; k < kRing; k += 2) {
+            consume(k);
+            raw[k] = In::load_vec(xp + (kRing + k) * kUnitBytes);
+            raw[k + 1] = In::load_vec(xp + (kRing + k + 1) * kUnitBytes);
+        }
+        xp += kRing * kUnitBytes;
+        qp += kRing * 32;
+        sp += kRing * 512;
+    }
+    // at most two more rounds: the first may still refill part of the ring
+#pragma unroll 1
+    for (; remaining > 0; remaining -= kRing) {
+#pragma unroll
+        for (int k = 0; k < kRing; k += 2) {
+            if (k < remaining) consume(k);                    // uniform
+            if (kRing + k < remaining) {                      // uniform; pairs are whole
+                raw[k] = In::load_vec(xp + (kRing + k) * kUnitBytes);
+                raw[k + 1] = In::load_vec(xp + (kRing + k + 1) * kUnitBytes);
+            }
+        }
+        xp += kRing * kUnitBytes;
+        qp += kRing * 32;
+        sp += kRing * 512;
+    }
+}
+
+// Edge segment: rows past the input, ragged columns, padding to 16x16 and to whole scale chunks.
+template <int DT, bool VEC, int VARIANT>
+__device__ __forceinline__ void walk_edge(const LaneCtx& c, int u_begin, int u_end) {
+    using In = Input<DT>;
+    using Raw = typename In::Raw;
+    const int sub = c.sub;
+    const bool odd = c.odd;
+
+    auto load_unit = [&](int cbg) -> Raw {
+        Raw v = In::zero();
+        const int c0 = cbg * 64 + sub * 8;
+        if (c.row_in && cbg < u_end && c0 < c.cols) {
+            if (VEC) {   // cols % 8 == 0 and 16-byte aligned base: the whole vector is inside the row
+                v = In::load_vec(c.x_row + c0 * In::kBytes);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (c0 + i < c.cols) In::set(v, i, c.x_row, c0 + i);
+            }
+        }
+        return v;
+    };
+
+    Raw raw[kRing];
+#pragma unroll
+    for (int k = 0; k < kRing; ++k) raw[k] = load_unit(u_begin + k);
+
+#pragma unroll 1
+    for (int base = u_begin; base < u_end; base += kRing) {
+#pragma unroll
+        for (int k = 0; k < kRing; k += 2) {
+            const int cbg_a = base + k;
+            const int cbg_b = cbg_a + 1;   // may be the segment's end: then unit B belongs to no one here
+            if (cbg_a < u_end) {           // uniform across the warp
+                const bool b_valid = cbg_b < u_end;
+                const int cbg_mine = odd ? cbg_b : cbg_a;
+                const bool mine_in = c.row_out && cbg_mine < u_end && cbg_mine * 64 + sub * 8 < c.pcol;
+                uint32_t word_a, word_b, s8;
+                quantize_pair<DT, VARIANT>(c, raw[k], raw[k + 1], mine_in, word_a, word_b, s8);
+                const int byte_col = cbg_a * 32 + sub * 4;
+                if (c.row_out && byte_col * 2 < c.pcol) *reinterpret_cast<uint32_t*>(c.q_row + byte_col) = word_a;
+                if (c.row_out && b_valid && (byte_col + 32) * 2 < c.pcol)
+                    *reinterpret_cast<uint32_t*>(c.q_row + byte_col + 32) = word_b;
+                const uint32_t sfw = gather_scale_word(s8, sub);
+                // lanes 0 and 1 of each group of eight store: lane 1 adds 512 bytes (unit B's chunk)
+                if (sub < 2 && (sub == 0 || b_valid))
+                    *reinterpret_cast<uint32_t*>(c.sf_row + (cbg_a + sub) * 512) = sfw;
+            }
+            raw[k] = load_unit(base + kRing + k);
+            raw[k + 1] = load_unit(base + kRing + k + 1);
+        }
+    }
+}
+
+// One warp walks a segment of one row group: it keeps kRing units in flight in registers and, each time it has
+// consumed a pair of units, issues the loads that refill those registers, so loads and arithmetic overlap inside
+// the warp and the bytes in flight per SM stay high for the whole life of the block.
+// Launch geometry: block (32, WX, WY) with WX * WY = kWarpsPerBlock; warp (wx, wy) of block (bx, by, bz) handles
+// segment bx*WX + wx of row group (bz*65535 + by)*WY + wy, so no thread divides anything.
+template <int DT, bool VEC, int VARIANT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(const QuantArgs a) {
+    using In = Input<DT>;
+    const int lane = threadIdx.x;
+    const int seg = blockIdx.x * blockDim.y + threadIdx.y;
+    const int group = (blockIdx.z * 65535 + blockIdx.y) * blockDim.z + threadIdx.z;
+    if (seg >= a.segments || group >= a.row_groups) return;   // whole warps
+    const int u_begin = seg * a.seg_units;
+    const int u_end = min(a.sf_cbg, u_begin + a.seg_units);
+    const int d4 = lane >> 3;
+    const int band = group >> 5;
+    const int d3 = group & 31;
+    const int r = band * 128 + d3 + 32 * d4;
+    LaneCtx c;
+    c.sub = lane & 7;
+    c.odd = c.sub & 1;
+    c.ts = __ldg(a.pts);
+    c.ts_in_range = c.ts >= 0x1p-60f && c.ts <= 0x1p60f;
+    c.rcp_ts = (VARIANT == 1 && c.ts_in_range) ? __frcp_rn(c.ts) : 0.0f;
+    c.row_in = r < a.rows;
+    c.row_out = r < a.prow;
+    c.hi_first = a.hi_first != 0;
+    c.cols = a.cols;
+    c.pcol = a.pcol;
+    c.x_row = (const char*)a.x + (int64_t)r * a.cols * In::kBytes;
+    c.q_row = a.q + (int64_t)r * (a.pcol >> 1);
+    c.sf_row = a.sf + (((int64_t)band * a.sf_cbg) * 32 + d3) * 16 + d4 * 4;
+    // rows of the warp are r0 + {0,32,64,96}: all inside the input iff the last one is; segments hold whole pairs
+    const bool interior = VEC && (band * 128 + d3 + 96 < a.rows) && (u_end * 64 <= a.cols) && ((u_end - u_begin) % 2 == 0);
+    if (interior) walk_interior<DT, VARIANT>(c, u_begin, u_end);
+    else walk_edge<DT, VEC, VARIANT>(c, u_begin, u_end);
+}
+
 template <int DT>
-int launch_quantize(const QuantArgs& a, bool vec, int variant, cudaStream_t stream) {
-    const int64_t tasks = a.row_groups * a.tasks_per_group;
-    const int64_t blocks = ceil_div64(tasks, kWarpsPerBlock);
-    if (blocks <= 0) return CK_B200_OK;
-    if (blocks > 0x7fffffffll) return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: tensor too large");
-    dim3 grid((unsigned)blocks), block(kWarpsPerBlock * 32);
+int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t stream) {
+    if (a.row_groups <= 0 || a.sf_cbg <= 0) return CK_B200_OK;
+    // Cut rows into segments of `su` units (even, at least the prefetch ring) so that the blocks fill whole waves
+    // of the 4 blocks an SM holds: among the candidates within 4 % of the best balance take the longest segment
+    // (longer walks amortise the per-warp set-up).
+    const int resident = 4 * sms;
+    int best_su = kRing, best_wx = 1;
+    double best_eff = -1.0;
+    for (int pass = 0; pass < 2; ++pass)
+    for (int su = kRing; ; su += 2) {
+        if (su > a.sf_cbg) su = (int)round_up64(a.sf_cbg, 2) < kRing ? kRing : (int)round_up64(a.sf_cbg, 2);
+        const int segs = (int)ceil_div64(a.sf_cbg, su);
+        // warps of a block side by side along the row while that idles no more than an eighth of them
+        int wx = kWarpsPerBlock;
+        while (wx > 1 && (int)round_up64(segs, wx) * 7 > segs * 8) wx >>= 1;
+        const int64_t ctas = ceil_div64(segs, wx) * ceil_div64(a.row_groups, kWarpsPerBlock / wx);
+        const double waves = (double)ctas / resident;
+        const double eff = waves / (double)ceil_div64(ctas, resident) * ((double)a.sf_cbg / ((double)segs * su)) *
+                           ((double)segs / (double)round_up64(segs, wx));
+        if (pass == 0) {
+            if (eff > best_eff) best_eff = eff;
+        } else if (eff >= 0.96 * best_eff) {
+            best_su = su;
+            best_wx = wx;
+        }
+        if (su >= a.sf_cbg || su >= 256) break;
+    }
+    a.seg_units = best_su;
+    a.segments = (int)ceil_div64(a.sf_cbg, best_su);
+    const int wx = best_wx;
+    const int wy = kWarpsPerBlock / wx;
+    const int64_t gy_total = ceil_div64(a.row_groups, wy);
+    dim3 block(32, wx, wy);
+    dim3 grid((unsigned)ceil_div64(a.segments, wx), (unsigned)(gy_total < 65535 ? gy_total : 65535),
+              (unsigned)ceil_div64(gy_total, 65535));
     if (vec) {
         if (variant == 0) quantize_nvfp4_kernel<DT, true, 0><<<grid, block, 0, stream>>>(a);
         else quantize_nvfp4_kernel<DT, true, 1><<<grid, block, 0, stream>>>(a);
@@ -367,7 +609,8 @@ using namespace ckb;
 extern "C" int ck_b200_quantize_nvfp4(const void* x_dev, int x_dtype, const float* per_tensor_scale_dev,
                                       void* q_out_dev, void* sf_out_dev, int64_t rows, int64_t cols, int pad_16x,
                                       int hi_first, void* stream) {
-    if (int rc = check_device(nullptr)) return rc;
+    int sms = 0;
+    if (int rc = check_device(&sms)) return rc;
     if (!x_dev || !per_tensor_scale_dev || !q_out_dev || !sf_out_dev)
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: null pointer");
     if (rows < 0 || cols < 0) return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: negative shape");
@@ -381,15 +624,16 @@ extern "C" int ck_b200_quantize_nvfp4(const void* x_dev, int x_dtype, const floa
     a.pts = per_tensor_scale_dev;
     a.q = (uint8_t*)q_out_dev;
     a.sf = (uint8_t*)sf_out_dev;
-    a.rows = rows;
-    a.cols = cols;
-    a.prow = pad_16x ? round_up64(rows, 16) : rows;
-    a.pcol = pad_16x ? round_up64(cols, 16) : cols;
-    a.row_groups = round_up64(a.prow, 128) / 4;
+    if (rows > 0x3fffff00ll || cols > 0x3fffff00ll)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: rows and cols must be below 2^30");
+    a.rows = (int)rows;
+    a.cols = (int)cols;
+    a.prow = (int)(pad_16x ? round_up64(rows, 16) : rows);
+    a.pcol = (int)(pad_16x ? round_up64(cols, 16) : cols);
+    a.row_groups = (int)(round_up64(a.prow, 128) / 4);
     const int64_t sf_cols = round_up64(a.pcol / 16, 4);
-    if (sf_cols / 4 > 0x3fffffff) return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: too many columns");
     a.sf_cbg = (int)(sf_cols / 4);
-    a.tasks_per_group = (int)ceil_div64(a.sf_cbg, kUnitsPerWarp);
+    a.seg_units = a.segments = 0;
     a.hi_first = hi_first ? 1 : 0;
     if (a.prow == 0 || a.pcol == 0) return CK_B200_OK;
     if (((uintptr_t)q_out_dev & 3) || ((uintptr_t)sf_out_dev & 3))
@@ -398,9 +642,9 @@ extern "C" int ck_b200_quantize_nvfp4(const void* x_dev, int x_dtype, const floa
     const int variant = g_quant_variant.load() ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (x_dtype) {
-        case CK_B200_DTYPE_F32: return launch_quantize<CK_B200_DTYPE_F32>(a, vec, variant, s);
-        case CK_B200_DTYPE_F16: return launch_quantize<CK_B200_DTYPE_F16>(a, vec, variant, s);
-        default: return launch_quantize<CK_B200_DTYPE_BF16>(a, vec, variant, s);
+        case CK_B200_DTYPE_F32: return launch_quantize<CK_B200_DTYPE_F32>(a, vec, variant, sms, s);
+        case CK_B200_DTYPE_F16: return launch_quantize<CK_B200_DTYPE_F16>(a, vec, variant, sms, s);
+        default: return launch_quantize<CK_B200_DTYPE_BF16>(a, vec, variant, sms, s);
     }
 }
 
