@@ -63,6 +63,7 @@ struct GemmArgs {
     int sfb_bands;        // 128-row bands in the B scale tensor
     int k_iters;          // ceil(K / 256)
     int m_tiles, n_tiles;
+    int raster_group;     // tiles are walked in groups of this many tile rows (all N tiles of a group before the next)
     int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
     int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
 };
@@ -259,6 +260,19 @@ __device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int 
     }
 }
 
+// Tile order: groups of `raster_group` tile rows; inside a group the tile row index runs fastest, then N.  The CTAs
+// that run concurrently then share a few A row blocks and a few B column blocks, so a group's A rows stay in L2
+// while B streams past them, instead of all of A cycling through L2 once per tile column.
+__device__ __forceinline__ void tile_coords(const GemmArgs& g, int tile, int& tm, int& tn) {
+    const int per_group = g.raster_group * g.n_tiles;
+    const int grp = tile / per_group;
+    const int within = tile - grp * per_group;
+    const int m0 = grp * g.raster_group;
+    const int rows = min(g.raster_group, g.m_tiles - m0);
+    tn = within / rows;
+    tm = m0 + (within - tn * rows);
+}
+
 // ---- kernel -----------------------------------------------------------------------------------------
 
 template <int BN, bool DBG>
@@ -318,7 +332,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         long long waited = 0;
         const long long t_begin = now();
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int tm = tile % g.m_tiles, tn = tile / g.m_tiles;
+            int tm, tn;
+            tile_coords(g, tile, tm, tn);
             int sfb_present = 0;
 #pragma unroll
             for (int b = 0; b < C::kBands; ++b)
@@ -442,7 +457,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         constexpr int kSteps = BN / EPI_COLS;
         constexpr int kOverlapSteps = C::kOverlapCols / EPI_COLS;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int tm = tile % g.m_tiles, tn = tile / g.m_tiles;
+            int tm, tn;
+            tile_coords(g, tile, tm, tn);
             const long long tw = now();
             ok = mbar_wait(smem_u32(&acc_full_bar[acc]), acc_phase, abort_flag, WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);
@@ -583,6 +599,11 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     }
     g.m_tiles = (int)ceil_div64(g.M, BM);
     g.n_tiles = (int)ceil_div64(g.N, BN);
+    // as many tile rows per group as keep the group's A rows (with room for B and the output) inside the 126 MB L2
+    const int64_t row_block_bytes = (int64_t)BM * (K / 2);
+    int64_t group = (32ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
+    if (group < 8) group = 8;
+    g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     kernel<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mb, mo, g);
@@ -640,6 +661,7 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     g.sfb_bands = (int)ceil_div64(N, 128);
     g.k_iters = (int)ceil_div64(K, 256);
     g.m_tiles = g.n_tiles = 0;
+    g.raster_group = 1;
     g.tma_store = 0;
     g.debug = g_gemm_debug.load();
     int variant = g_gemm_variant.load();
