@@ -470,16 +470,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * C::kAcc1Col;
             // accumulator 0 shares its last columns with accumulator 1's first ones: drain those first
             const int first_step = (C::kOverlapCols > 0 && acc == 0) ? kSteps - kOverlapSteps : 0;
-#pragma unroll 1
-            for (int i = 0; i < kSteps; ++i) {
-                const int s = (first_step + i) % kSteps;
-                uint32_t v[32];
-                tc_ld32(t_acc + s * EPI_COLS, v);
-                tc_wait_ld();
-                if (C::kOverlapCols > 0 && i == kOverlapSteps - 1) {   // shared columns are in registers now
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(overlap_bar));
-                }
+            auto emit = [&](int s, const uint32_t (&v)[32]) {
                 const int n0 = tn * BN + s * EPI_COLS;
                 float y[32];
                 scale_row32(g, n0, v, alpha, y);
@@ -508,6 +499,30 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 } else if (row < g.M && n0 < g.N) {
                     store_row32(g, row, n0, y);
                 }
+            };
+            int i = 0;
+            if (C::kOverlapCols > 0) {
+                // both steps of the shared columns are fetched before anything else so that they can be handed to
+                // the next tile's MMAs as early as possible
+                static_assert(C::kOverlapCols == 0 || kOverlapSteps == 2, "two epilogue steps cover the shared columns");
+                uint32_t v0[32], v1[32];
+                const int s0 = first_step % kSteps, s1 = (first_step + 1) % kSteps;
+                tc_ld32(t_acc + s0 * EPI_COLS, v0);
+                tc_ld32(t_acc + s1 * EPI_COLS, v1);
+                tc_wait_ld();
+                tc_fence_before();
+                mbar_arrive(smem_u32(overlap_bar));
+                emit(s0, v0);
+                emit(s1, v1);
+                i = 2;
+            }
+#pragma unroll 1
+            for (; i < kSteps; ++i) {
+                const int s = (first_step + i) % kSteps;
+                uint32_t v[32];
+                tc_ld32(t_acc + s * EPI_COLS, v);
+                tc_wait_ld();
+                emit(s, v);
             }
             tc_fence_before();
             mbar_arrive(smem_u32(&acc_empty_bar[acc]));
@@ -526,6 +541,332 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols)
                      : "memory");
+    }
+}
+
+// ---- 2-CTA kernel ---------------------------------------------------------------------------------
+//
+// The same pipeline on pairs of CTAs (thread-block clusters of 2, tcgen05 cta_group::2): a pair computes a
+// 256 x 256 tile.  CTA r of the pair loads A rows [128 r, 128 r + 128) of the tile, HALF of the B tile (its rows
+// [128 r, 128 r + 128) of N), its own 128 rows of A scales and all 256 rows of B scales; one MMA instruction issued
+// by CTA 0 runs on both SMs (each reads the other half of B from its peer's shared memory) and each CTA keeps the
+// fp32 accumulators of its 128 rows x 256 columns in its own tensor memory.  Per SM and 256 K-elements that is
+// 38 KB of loads instead of 54 KB, which is what the 1-CTA kernel's main loop waits for.
+//   * Loads of both CTAs signal CTA 0's "full" barrier (TMA .cta_group::2 lets the mbarrier live in the peer CTA);
+//     none of them is a multicast load.
+//   * CTA 0's MMA warp frees a stage, and publishes an accumulator, in both CTAs with one tcgen05.commit per CTA.
+//   * Epilogue warps of both CTAs report drained accumulators to CTA 0 with remote mbarrier arrives.
+// Scale chunks are fetched as 2-D tiles (a [chunks, 128 x u32] view of the tiled scale tensor, box of 4 chunks).
+
+constexpr int kStages2 = 5;
+constexpr int kA2 = BM * BK_BYTES;                 // 16 KiB: this CTA's 128 rows of A
+constexpr int kB2 = 128 * BK_BYTES;                // 16 KiB: this CTA's half of the 256 B rows
+constexpr int kSfa2 = CHUNKS * SF_CHUNK_BYTES;     // 2 KiB
+constexpr int kSfb2 = 2 * CHUNKS * SF_CHUNK_BYTES; // 4 KiB: both 128-row bands of the B tile
+constexpr int kStageBytes2 = kA2 + kB2 + kSfa2 + kSfb2;   // 38 KiB
+constexpr int kStagingBytes2 = 4 * 2 * STAGING_BYTES_PER_WARP;   // two staging tiles per epilogue warp
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kStagingBytes2 + 1024 + 256;
+constexpr int kAccCol1_2 = 192, kSfCol0_2 = 448, kSfRegion2 = 24;   // tensor-memory plan of the BN = 256 kernel
+constexpr uint32_t kIdesc2 = (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+static_assert(kSmemBytes2 <= 232448, "shared memory budget");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa_tmem,
+                                            uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+
+template <bool DBG>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                       const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* staging = smem + kStages2 * kStageBytes2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes2);
+    uint64_t* full_bar = bars;                       // [kStages2] used in CTA 0: loads of both CTAs -> MMA
+    uint64_t* empty_bar = bars + kStages2;           // [kStages2] in each CTA: MMA -> this CTA's producer
+    uint64_t* acc_full_bar = bars + 2 * kStages2;    // [2] in each CTA: MMA -> this CTA's epilogue
+    uint64_t* acc_empty_bar = acc_full_bar + 2;      // [2] used in CTA 0: epilogues of both CTAs -> MMA
+    uint64_t* overlap_bar = acc_empty_bar + 2;       // [1] used in CTA 0
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(overlap_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 2);     // one expect_tx arrive from each CTA's producer
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&acc_full_bar[s]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[s]), 8);   // one arrive per epilogue warp of both CTAs
+        }
+        mbar_init(smem_u32(overlap_bar), 8);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs allocates the pair's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();   // barriers of both CTAs are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = g.m_tiles * g.n_tiles;   // 256 x 256 tiles
+    auto now = [] { return DBG ? clock64() : 0ll; };
+
+    if (warp == 0) {
+        // ---------------- producer (both CTAs) ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        long long waited = 0;
+        const long long t_begin = now();
+        const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);   // CTA 0's barriers
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            int tm, tn;
+            tile_coords(g, tile, tm, tn);
+            const int a_row = (tm * 2 + (int)rank) * BM;                 // this CTA's A rows; also its scale band
+            const int b_row = tn * 256 + (int)rank * 128;                // this CTA's half of the B tile
+            const int sfa_chunk0 = (tm * 2 + (int)rank) * g.sf_cbg;
+            const int sfb_chunk0 = tn * 2 * g.sf_cbg;
+            for (int kb = 0; kb < g.k_iters; ++kb) {
+                const long long t0 = now();
+                ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                waited += now() - t0;
+                if (!ok) break;
+                const uint32_t st = smem_u32(smem) + stage * kStageBytes2;
+                const uint32_t bar = full0 + stage * 8;
+                if (elect_one()) {
+                    mbar_expect_tx_cluster(bar, kStageBytes2);   // every box is transferred in full (zero fill past the ends)
+                    tma_load_2d_pair(st, &tmap_a, kb * BK_BYTES, a_row, bar);
+                    tma_load_2d_pair(st + kA2, &tmap_b, kb * BK_BYTES, b_row, bar);
+                    tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * CHUNKS, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * CHUNKS, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * CHUNKS, bar);
+                }
+                __syncwarp();
+                if (++stage == kStages2) { stage = 0; phase ^= 1; }
+            }
+        }
+        if (DBG && pair == 0 && lane == 0)
+            printf("[gemm pair cta%u] producer: total %lld cycles, waiting for free stages %lld\n", rank, now() - t_begin,
+                   waited);
+    } else if (warp == 1 && rank == 0) {
+        // ---------------- MMA issuer (CTA 0 of the pair) ----------------
+        int stage = 0, acc = 0, local_tile = 0;
+        uint32_t phase = 0, acc_phase = 0;
+        bool ok = true;
+        long long wait_acc = 0, wait_full = 0;
+        const long long t_begin = now();
+        const uint32_t smem_enc = (smem_u32(smem) >> 4) & 0x3fffu;
+        const uint32_t sf_t0 = tmem_base + kSfCol0_2;
+        const uint32_t empty_peer = map_to_cta(smem_u32(&empty_bar[0]), 1);
+        const uint32_t acc_full_peer = map_to_cta(smem_u32(&acc_full_bar[0]), 1);
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local_tile) {
+            long long t0 = now();
+            ok = mbar_wait(smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1, abort_flag, WAIT_ACC_EMPTY);
+            if (local_tile > 0 && ok)
+                ok = mbar_wait(smem_u32(overlap_bar), (uint32_t)(local_tile - 1) & 1u, abort_flag, WAIT_OVERLAP);
+            ok = __all_sync(0xffffffffu, ok);
+            wait_acc += now() - t0;
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * kAccCol1_2;
+            for (int kb = 0; kb < g.k_iters; ++kb) {
+                t0 = now();
+                ok = mbar_wait(smem_u32(&full_bar[0]) + stage * 8, phase, abort_flag, WAIT_STAGE_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                wait_full += now() - t0;
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t st_enc = smem_enc + stage * (kStageBytes2 >> 4);
+                const uint32_t a_lo = st_enc | kOperandDescLoFlags;
+                const uint32_t b_lo = a_lo + (kA2 >> 4);
+                const uint32_t sfa_lo = st_enc + ((kA2 + kB2) >> 4);
+                const uint32_t sfb_lo = sfa_lo + (kSfa2 >> 4);
+                const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                if (elect_one()) {
+#pragma unroll
+                    for (int j = 0; j < CHUNKS; ++j) {
+                        if (j < nchunk) {
+                            const uint32_t sfa_t = sf_t0 + (j >> 1) * kSfRegion2 + (j & 1) * 4;
+                            const uint32_t sfb_t = sf_t0 + (j >> 1) * kSfRegion2 + 8 + (j & 1) * 8;
+                            tc_cp_sf_pair(sfa_t, desc64(sfa_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
+                            tc_cp_sf_pair(sfb_t, desc64(sfb_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
+                            tc_cp_sf_pair(sfb_t + 4, desc64(sfb_lo + (kSfa2 + j * SF_CHUNK_BYTES) / 16, kSfDescHi));
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < CHUNKS; ++j) {
+                        if (j < nchunk) {
+                            const uint32_t sfa_t = sf_t0 + (j >> 1) * kSfRegion2 + (j & 1) * 4;
+                            const uint32_t sfb_t = sf_t0 + (j >> 1) * kSfRegion2 + 8 + (j & 1) * 8;
+                            tc_mma_pair(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
+                                        kIdesc2, sfa_t, sfb_t, (j != 0 || kb != 0) ? 1u : 0u);
+                        }
+                    }
+                    tc_commit_pair(smem_u32(&empty_bar[0]) + stage * 8);   // this CTA's producer
+                    tc_commit_pair(empty_peer + stage * 8);                // the peer's producer
+                }
+                __syncwarp();
+                if (++stage == kStages2) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+            if (elect_one()) {
+                tc_commit_pair(smem_u32(&acc_full_bar[acc]));
+                tc_commit_pair(acc_full_peer + acc * 8);
+            }
+            __syncwarp();
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+        if (DBG && pair == 0 && lane == 0)
+            printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n",
+                   now() - t_begin, wait_acc, wait_full);
+    } else if (warp >= 2) {
+        // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+        const int quad = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0, buf = 0;
+        bool ok = true;
+        long long wait_acc = 0;
+        const long long t_begin = now();
+        const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
+        uint8_t* my_staging = staging + quad * 2 * STAGING_BYTES_PER_WARP;
+        const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
+        const uint32_t overlap0 = map_to_cta(smem_u32(overlap_bar), 0);
+        constexpr int kSteps = 256 / EPI_COLS;
+        constexpr int kOverlapSteps = 64 / EPI_COLS;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            int tm, tn;
+            tile_coords(g, tile, tm, tn);
+            const long long tw = now();
+            ok = mbar_wait(smem_u32(&acc_full_bar[acc]), acc_phase, abort_flag, WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            wait_acc += now() - tw;
+            if (!ok) break;
+            tc_fence_after();
+            const int row0 = (tm * 2 + (int)rank) * BM + quad * 32;
+            const int64_t row = (int64_t)row0 + lane;
+            const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccCol1_2;
+            const int first_step = (acc == 0) ? kSteps - kOverlapSteps : 0;
+            auto emit = [&](int s, const uint32_t (&v)[32]) {
+                const int n0 = tn * 256 + s * EPI_COLS;
+                float y[32];
+                scale_row32(g, n0, v, alpha, y);
+                if (g.tma_store) {
+                    if (lane == 0) tma_store_wait_read<1>();   // the store issued two steps ago has read its tile
+                    __syncwarp();
+                    uint8_t* tile_smem = my_staging + buf * STAGING_BYTES_PER_WARP;
+                    uint8_t* rowp = tile_smem + lane * 64;
+                    const int sw = (lane >> 1) & 3;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        uint4 o;
+                        o.x = pack16(y[8 * p + 0], y[8 * p + 1], g.out_dtype);
+                        o.y = pack16(y[8 * p + 2], y[8 * p + 3], g.out_dtype);
+                        o.z = pack16(y[8 * p + 4], y[8 * p + 5], g.out_dtype);
+                        o.w = pack16(y[8 * p + 6], y[8 * p + 7], g.out_dtype);
+                        *reinterpret_cast<uint4*>(rowp + ((p ^ sw) << 4)) = o;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && n0 < g.N && row0 < g.M) {
+                        tma_store_2d(&tmap_out, n0, row0, smem_u32(tile_smem));
+                        tma_store_commit();
+                    }
+                    buf ^= 1;
+                } else if (row < g.M && n0 < g.N) {
+                    store_row32(g, row, n0, y);
+                }
+            };
+            {
+                // both steps of the columns shared by the two accumulators are fetched first and handed to the
+                // next tile's MMAs before any output work
+                static_assert(kOverlapSteps == 2, "two epilogue steps cover the shared columns");
+                uint32_t v0[32], v1[32];
+                const int s0 = first_step % kSteps, s1 = (first_step + 1) % kSteps;
+                tc_ld32(t_acc + s0 * EPI_COLS, v0);
+                tc_ld32(t_acc + s1 * EPI_COLS, v1);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(overlap0);
+                emit(s0, v0);
+                emit(s1, v1);
+            }
+#pragma unroll 1
+            for (int i = 2; i < kSteps; ++i) {
+                const int s = (first_step + i) % kSteps;
+                uint32_t v[32];
+                tc_ld32(t_acc + s * EPI_COLS, v);
+                tc_wait_ld();
+                emit(s, v);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+        if (g.tma_store && lane == 0) tma_store_wait_all();
+        if (DBG && pair == 0 && threadIdx.x == 64)
+            printf("[gemm pair cta%u] epilogue: total %lld cycles, waiting for accumulators %lld\n", rank, now() - t_begin,
+                   wait_acc);
+    }
+
+    tc_fence_before();
+    cluster_sync_all();   // no CTA of the pair leaves while the other may still read its shared memory or signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -579,6 +920,85 @@ int make_output_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N) {
     return CK_B200_OK;
 }
 
+// Tiled scale tensor seen as [chunks, 128 x u32] (one 512-byte chunk per row), boxes of 4 chunks, no swizzle.
+int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {128, (cuuint64_t)chunks};
+    cuuint64_t strides[1] = {(cuuint64_t)SF_CHUNK_BYTES};
+    cuuint32_t box[2] = {128, (cuuint32_t)CHUNKS};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+    return CK_B200_OK;
+}
+
+// Pairs of CTAs that can be resident at once (clusters of 2 need two free SMs of one GPC), cached per device.
+int max_active_pairs(int* out) {
+    static std::mutex mu;
+    static int cache[64] = {0};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == 0) {
+        auto kernel = gemm_nvfp4_pair_kernel<false>;
+        CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 148);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = kSmemBytes2;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        CKB_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, (const void*)kernel, &cfg));
+        cache[dev] = n > 0 ? n : -1;
+    }
+    if (cache[dev] < 0) return fail(CK_B200_ERR_CUDA, "no CTA pair of the GEMM kernel fits on this device");
+    *out = cache[dev];
+    return CK_B200_OK;
+}
+
+int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream) {
+    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<true> : gemm_nvfp4_pair_kernel<false>;
+    int pairs = 0;
+    if (int rc = max_active_pairs(&pairs)) return rc;
+    cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+    if (attr_err != cudaSuccess)
+        return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
+                    cudaGetErrorString(attr_err));
+    CUtensorMap ma, mb, msa, msb, mo;
+    if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM)) return rc;
+    if (int rc = make_operand_map(&mb, b, g.N, K / 2, 128)) return rc;
+    if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg)) return rc;
+    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg)) return rc;
+    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
+    if (g.tma_store) {
+        if (int rc = make_output_map(&mo, g.out, g.M, g.N)) return rc;
+    } else {
+        mo = ma;   // not used by the kernel
+    }
+    g.m_tiles = (int)ceil_div64(g.M, 256);
+    g.n_tiles = (int)ceil_div64(g.N, 256);
+    const int64_t row_block_bytes = 256ll * (K / 2);
+    int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
+    if (group < 4) group = 4;
+    g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
+    const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
+    const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
+    kernel<<<grid, NUM_THREADS, kSmemBytes2, stream>>>(ma, mb, msa, msb, mo, g);
+    g_launches.fetch_add(1);
+    CKB_CUDA_OK(cudaGetLastError());
+    return CK_B200_OK;
+}
+
 template <int BN>
 int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream) {
     using C = Cfg<BN>;
@@ -601,7 +1021,7 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     g.n_tiles = (int)ceil_div64(g.N, BN);
     // as many tile rows per group as keep the group's A rows (with room for B and the output) inside the 126 MB L2
     const int64_t row_block_bytes = (int64_t)BM * (K / 2);
-    int64_t group = (32ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
+    int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 8) group = 8;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
@@ -665,8 +1085,11 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     g.tma_store = 0;
     g.debug = g_gemm_debug.load();
     int variant = g_gemm_variant.load();
-    if (variant == 0) variant = (N > 128) ? 2 : 1;   // 128x256 tiles halve the operand traffic per flop
+    // CTA pairs with 256x256 tiles when the problem has more than one tile row and column; otherwise one CTA per
+    // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
+    if (variant == 0) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
+    if (variant == 3) return launch_gemm_pair(a_dev, b_dev, g, K, s);
     if (variant == 2) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s);
     return launch_gemm<128>(a_dev, b_dev, g, K, sms, s);
 }
