@@ -64,6 +64,9 @@ struct GemmArgs {
     int k_iters;          // ceil(K / 256)
     int m_tiles, n_tiles;
     int raster_group;     // tiles are walked in groups of this many tile rows (all N tiles of a group before the next)
+    int splits;           // split-K: every tile is computed by `splits` work items over k_per_split stages each,
+    int k_per_split;      //          which leave fp32 partial sums in `partial` for splitk_reduce_kernel
+    float* partial;       // [splits, M, N] fp32 scratch (split-K only)
     int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
     int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
 };
@@ -320,7 +323,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = g.m_tiles * g.n_tiles;
+    const int total_items = g.m_tiles * g.n_tiles * g.splits;
     // cycle counters of the debug build (DBG): compiled out otherwise
     auto now = [] { return DBG ? clock64() : 0ll; };
 
@@ -331,7 +334,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         bool ok = true;
         long long waited = 0;
         const long long t_begin = now();
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const int tile = item / g.splits;
+            const int kb0 = (item - tile * g.splits) * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);
             int tm, tn;
             tile_coords(g, tile, tm, tn);
             int sfb_present = 0;
@@ -340,7 +345,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (tn * C::kBands + b < g.sfb_bands) ++sfb_present;
             const uint8_t* sfa_src = g.sfa + (int64_t)tm * g.sf_cbg * SF_CHUNK_BYTES;
             const uint8_t* sfb_src = g.sfb + (int64_t)tn * C::kBands * g.sf_cbg * SF_CHUNK_BYTES;
-            for (int kb = 0; kb < g.k_iters; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 const long long t0 = now();
                 ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
@@ -377,7 +382,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const long long t_begin = now();
         const uint32_t smem_enc = smem_u32(smem) >> 4;   // descriptor addresses are in 16-byte units
         const uint32_t sf_t0 = tmem_base + C::kSfCol0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local_tile) {
+            const int kb0 = (item % g.splits) * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);
             long long t0 = now();
             // the accumulator's own columns: drained by the epilogue two tiles ago
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1, abort_flag, WAIT_ACC_EMPTY);
@@ -389,7 +395,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * C::kAcc1Col;
-            for (int kb = 0; kb < g.k_iters; ++kb) {
+            for (int kb = kb0; kb < kb1; ++kb) {
                 t0 = now();
                 ok = mbar_wait(smem_u32(&full_bar[0]) + stage * 8, phase, abort_flag, WAIT_STAGE_FULL);
                 ok = __all_sync(0xffffffffu, ok);
@@ -426,7 +432,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                 sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
                             // 64 elements of K = 32 bytes = 2 descriptor address units inside the swizzle row
                             tc_mma(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
-                                   C::kIdesc, sfa_t, sfb_t, (j != 0 || kb != 0) ? 1u : 0u);
+                                   C::kIdesc, sfa_t, sfb_t, (j != 0 || kb != kb0) ? 1u : 0u);
                         }
                     }
                     tc_commit(smem_u32(&empty_bar[0]) + stage * 8);   // stage reusable once these MMAs have read it
@@ -456,7 +462,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t my_staging_u32 = smem_u32(my_staging);
         constexpr int kSteps = BN / EPI_COLS;
         constexpr int kOverlapSteps = C::kOverlapCols / EPI_COLS;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const int tile = item / g.splits;
+            const int split = item - tile * g.splits;
             int tm, tn;
             tile_coords(g, tile, tm, tn);
             const long long tw = now();
@@ -472,6 +480,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int first_step = (C::kOverlapCols > 0 && acc == 0) ? kSteps - kOverlapSteps : 0;
             auto emit = [&](int s, const uint32_t (&v)[32]) {
                 const int n0 = tn * BN + s * EPI_COLS;
+                if (g.splits > 1) {   // split-K: raw fp32 partial sums; alpha, bias and rounding happen in the reduction
+                    if (row < g.M && n0 < g.N) {
+                        float* p = g.partial + ((int64_t)split * g.M + row) * g.N + n0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (n0 + 4 * j < g.N)
+                                *reinterpret_cast<uint4*>(p + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                    return;
+                }
                 float y[32];
                 scale_row32(g, n0, v, alpha, y);
                 if (g.tma_store) {
@@ -870,6 +888,37 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     }
 }
 
+// ---- split-K reduction ----------------------------------------------------------------------------
+
+// out[m,n] = out_dtype( alpha * sum_s partial[s,m,n] + bias[n] ), four columns per thread (N % 8 == 0).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                                            const float* tsa, const float* tsb, const float* alpha_ptr,
+                                                            const void* bias, int bias_dtype, void* out, int out_dtype) {
+    const int64_t quads = (int64_t)M * N / 4;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= quads) return;
+    const float alpha = alpha_ptr ? __ldg(alpha_ptr) : __fmul_rn(__ldg(tsa), __ldg(tsb));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (int64_t)s * quads + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float y[4] = {acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha};
+    const int n = (int)((i * 4) % N);
+    if (bias) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] += bias_at(bias, bias_dtype, n + j);
+    }
+    if (out_dtype == CK_B200_DTYPE_F32) {
+        reinterpret_cast<float4*>(out)[i] = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+        uint2 o;
+        o.x = pack16(y[0], y[1], out_dtype);
+        o.y = pack16(y[2], y[3], out_dtype);
+        reinterpret_cast<uint2*>(out)[i] = o;
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -991,6 +1040,9 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 4) group = 4;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
+    g.splits = 1;
+    g.k_per_split = g.k_iters;
+    g.partial = nullptr;
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
     kernel<<<grid, NUM_THREADS, kSmemBytes2, stream>>>(ma, mb, msa, msb, mo, g);
@@ -999,8 +1051,19 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     return CK_B200_OK;
 }
 
+// Split-K factor for a problem with one tile row (M <= 128): as many work items as SMs, at least two stages per
+// item, and partial sums that fit the scratch buffer.
+int choose_splits(int n_tiles, int k_iters, int sms, int64_t M, int64_t N, size_t scratch_bytes) {
+    int s = sms / (n_tiles > 0 ? n_tiles : 1);
+    if (s > k_iters / 2) s = k_iters / 2;
+    if (s > 16) s = 16;
+    while (s > 1 && (size_t)s * (size_t)M * (size_t)N * 4 > scratch_bytes) --s;
+    return s < 1 ? 1 : s;
+}
+
 template <int BN>
-int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream) {
+int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream, float* scratch,
+                size_t scratch_bytes) {
     using C = Cfg<BN>;
     auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true> : gemm_nvfp4_kernel<BN, false>;
     // opting in to large dynamic shared memory is per function and per device; doing it on every call is cheap
@@ -1024,11 +1087,29 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 8) group = 8;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
-    const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
-    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    g.splits = 1;
+    g.k_per_split = g.k_iters;
+    g.partial = nullptr;
+    if (g.m_tiles == 1 && scratch != nullptr) {
+        g.splits = choose_splits(g.n_tiles, g.k_iters, sms, g.M, g.N, scratch_bytes);
+        if (g.splits > 1) {
+            g.k_per_split = (int)ceil_div64(g.k_iters, g.splits);
+            g.splits = (int)ceil_div64(g.k_iters, g.k_per_split);   // no empty work items
+            g.partial = scratch;
+        }
+    }
+    const int64_t items = (int64_t)g.m_tiles * g.n_tiles * g.splits;
+    const unsigned grid = (unsigned)(items < sms ? items : sms);
     kernel<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(cudaGetLastError());
+    if (g.splits > 1) {
+        const int64_t quads = (int64_t)g.M * g.N / 4;
+        splitk_reduce_kernel<<<(unsigned)ceil_div64(quads, 256), 256, 0, stream>>>(
+            g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias, g.bias_dtype, g.out, g.out_dtype);
+        g_launches.fetch_add(1);
+        CKB_CUDA_OK(cudaGetLastError());
+    }
     return CK_B200_OK;
 }
 
@@ -1037,13 +1118,11 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
 
 using namespace ckb;
 
-extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
-                                       const float* tensor_scale_a_dev, const float* tensor_scale_b_dev,
-                                       const float* alpha_dev_or_null, const void* bias_dev_or_null, int bias_dtype,
-                                       void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace_dev,
-                                       size_t workspace_bytes, void* stream) {
-    (void)workspace_dev;
-    (void)workspace_bytes;
+namespace {
+int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                   const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
+                   const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N,
+                   int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream) {
     int sms = 0;
     if (int rc = check_device(&sms)) return rc;
     if (!a_dev || !sfa_dev || !b_dev || !sfb_dev || !out_dev)
@@ -1081,6 +1160,9 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     g.sfb_bands = (int)ceil_div64(N, 128);
     g.k_iters = (int)ceil_div64(K, 256);
     g.m_tiles = g.n_tiles = 0;
+    g.splits = 1;
+    g.k_per_split = g.k_iters;
+    g.partial = nullptr;
     g.raster_group = 1;
     g.tma_store = 0;
     g.debug = g_gemm_debug.load();
@@ -1089,10 +1171,25 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
     // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
     if (variant == 0) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
-    if (variant == 3) return launch_gemm_pair(a_dev, b_dev, g, K, s);
-    if (variant == 2) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s);
-    return launch_gemm<128>(a_dev, b_dev, g, K, sms, s);
+    if (workspace_dev && ((uintptr_t)workspace_dev & 15))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
+    float* scratch = (float*)workspace_dev;
+    if (variant == 3 && M > 128) return launch_gemm_pair(a_dev, b_dev, g, K, s);
+    if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    // one tile row: 128-column tiles give the most work items, and split-K (with scratch) fills the remaining SMs
+    return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
 }
+}  // namespace
+
+extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                                       const float* tensor_scale_a_dev, const float* tensor_scale_b_dev,
+                                       const float* alpha_dev_or_null, const void* bias_dev_or_null, int bias_dtype,
+                                       void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace_dev,
+                                       size_t workspace_bytes, void* stream) {
+    return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
+                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, workspace_dev, workspace_bytes, stream);
+}
+
 
 extern "C" int ck_b200_read_device_status(int* status_out) {
     if (int rc = check_device(nullptr)) return rc;

@@ -16,6 +16,21 @@ from . import _lib
 DTYPE_TO_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}  # eager/quantization.py:34-42
 
 
+_WORKSPACES: dict[int, torch.Tensor] = {}
+_WORKSPACE_BYTES = 32 << 20   # the reference keeps a 32 MiB cuBLAS workspace per device (backends/cuda/__init__.py:444-462)
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    """Per-device scratch for split-K partial sums (problems with M <= 128), allocated once through torch's caching
+    allocator so that calls stay allocation-free afterwards."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _WORKSPACES.get(idx)
+    if ws is None:
+        ws = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _WORKSPACES[idx] = ws
+    return ws
+
+
 def roundup(x: int, multiple: int) -> int:
     return ((x + multiple - 1) // multiple) * multiple
 
@@ -159,9 +174,11 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
         if out.numel() == 0:
             return out
+        ws = _workspace(a.device) if m <= 128 else None
         rc = _lib.load().ck_b200_scaled_mm_nvfp4(_ptr(a), _ptr(block_scale_a), _ptr(b), _ptr(block_scale_b), _ptr(tsa),
                                                  _ptr(tsb), _ptr(alpha_t), _ptr(bias), bias_code, _ptr(out),
-                                                 DTYPE_TO_CODE[out_dtype], m, n, k, None, 0, _stream(a.device))
+                                                 DTYPE_TO_CODE[out_dtype], m, n, k, _ptr(ws),
+                                                 0 if ws is None else ws.numel(), _stream(a.device))
     _lib.check(rc, "scaled_mm_nvfp4")
     return out
 

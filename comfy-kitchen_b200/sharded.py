@@ -66,6 +66,19 @@ class ShardedNVFP4Linear:
                                      bias=self.bias, out_dtype=x.dtype if x.dtype != torch.float32 else torch.bfloat16)
         return y[: x.shape[0], : self.local_rows]
 
+    def gather_async(self, y_local: torch.Tensor):
+        """Start the all-gather of equal column blocks and return ``(work, buffer)``: the collective runs on the
+        process group's own stream, so kernels enqueued afterwards overlap it; ``work.wait()`` orders the current
+        stream after it.  The buffer is rank-major [G, M, N/G]."""
+        m = y_local.shape[0]
+        sizes = {b - a for a, b in (shard_rows(self.out_features, self.world, r) for r in range(self.world))}
+        if len(sizes) != 1:
+            raise ValueError("gather_async needs equal shards")
+        y_local = y_local.contiguous()
+        flat = torch.empty((self.world * m, y_local.shape[1]), dtype=y_local.dtype, device=y_local.device)
+        work = dist.all_gather_into_tensor(flat, y_local, group=self.group, async_op=True)
+        return work, flat.view(self.world, m, y_local.shape[1])
+
     def gather(self, y_local: torch.Tensor, row_major: bool = True) -> torch.Tensor:
         """All-gather the column blocks.  ``row_major=False`` returns the rank-major [G, M, N/G] buffer the
         collective produces (equal shards only) and skips the re-layout pass."""
