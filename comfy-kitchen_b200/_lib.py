@@ -15,6 +15,7 @@ EXPORTED_SYMBOLS = (
     "ck_b200_quantize_nvfp4",
     "ck_b200_dequantize_nvfp4",
     "ck_b200_scaled_mm_nvfp4",
+    "ck_b200_scaled_mm_nvfp4_static_scratch",
     "ck_b200_dynamic_scale_nvfp4",
     "ck_b200_last_error",
     "ck_b200_query",
@@ -47,6 +48,8 @@ def load() -> ctypes.CDLL:
     L.ck_b200_dequantize_nvfp4.restype = i32
     L.ck_b200_scaled_mm_nvfp4.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i64, i64, i64, vp, sz, vp]
     L.ck_b200_scaled_mm_nvfp4.restype = i32
+    L.ck_b200_scaled_mm_nvfp4_static_scratch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i64, i64, i64, vp]
+    L.ck_b200_scaled_mm_nvfp4_static_scratch.restype = i32
     L.ck_b200_dynamic_scale_nvfp4.argtypes = [vp, i32, i64, vp, vp]
     L.ck_b200_dynamic_scale_nvfp4.restype = i32
     L.ck_b200_last_error.argtypes = []

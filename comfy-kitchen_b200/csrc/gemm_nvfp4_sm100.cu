@@ -1191,6 +1191,55 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
 }
 
 
+// ---- entry point with built-in scratch --------------------------------------------------------------
+
+namespace {
+constexpr size_t kStaticScratchBytes = 8u << 20;
+// Split-K partial sums for callers that cannot hand over device memory of their own.  Lives in the library image:
+// every device that loads the library holds these 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device, looked up once per device.  In host code the array's
+// name is only a handle for the runtime, not a device pointer, so it is never passed to a kernel directly.
+int static_scratch_address(float** out) {
+    static std::mutex mu;
+    static void* cache[64] = {nullptr};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(CK_B200_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        cache[dev] = p;
+    }
+    *out = reinterpret_cast<float*>(cache[dev]);
+    return CK_B200_OK;
+}
+}  // namespace
+
+extern "C" int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const void* sfa_dev, const void* b_dev,
+                                                      const void* sfb_dev, const float* tensor_scale_a_dev,
+                                                      const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
+                                                      const void* bias_dev_or_null, int bias_dtype, void* out_dev,
+                                                      int out_dtype, int64_t M, int64_t N, int64_t K, void* stream) {
+    if (M > 128)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT,
+                    "scaled_mm_nvfp4_static_scratch: M = %lld is beyond the limit of 128 rows (larger problems need no "
+                    "scratch: use ck_b200_scaled_mm_nvfp4)", (long long)M);
+    if (M > 0 && N > 0 && (size_t)M * (size_t)N * 4 * 2 > kStaticScratchBytes)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT,
+                    "scaled_mm_nvfp4_static_scratch: M * N = %lld is beyond the limit of %lld outputs (two fp32 partial "
+                    "sums per output must fit the %lld-byte built-in scratch)",
+                    (long long)(M * N), (long long)(kStaticScratchBytes / 8), (long long)kStaticScratchBytes);
+    float* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
+                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, scratch, kStaticScratchBytes, stream);
+}
+
 extern "C" int ck_b200_read_device_status(int* status_out) {
     if (int rc = check_device(nullptr)) return rc;
     if (!status_out) return fail(CK_B200_ERR_INVALID_ARGUMENT, "read_device_status: null pointer");

@@ -82,6 +82,29 @@ int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* 
                             size_t workspace_bytes, void* stream);
 
 /*
+ * scaled_mm_nvfp4 for small M with the split-K scratch built into the library.  No counterpart in the reference.
+ *
+ * Who needs it: code that may launch kernels but may not obtain device memory at the point of the call - a plugin
+ * running inside another framework's captured or pre-planned execution, a real-time loop with a frozen memory plan,
+ * a host that keeps the CUDA allocator to itself.  Such callers have no workspace to pass to
+ * ck_b200_scaled_mm_nvfp4, and without one a problem with M <= 128 runs unsplit on a fraction of the SMs.
+ * Here the fp32 partial sums go to an 8 MiB array that is part of the library image (every GPU that loads the
+ * library holds it until the process exits); the call itself performs no allocation of any kind.
+ *
+ * Same arguments and result as ck_b200_scaled_mm_nvfp4 minus the workspace.  Limits, rejected with
+ * CK_B200_ERR_INVALID_ARGUMENT and a message: M <= 128, and M * N <= 1 048 576 outputs (two partial sums each).
+ * The first call on each device looks the array's device address up (with that device current): make that call
+ * before starting a stream capture.  All calls share the one array and it is not cleared between calls (every word
+ * that is read has been written by the same call first): two such calls that overlap on the GPU - different streams,
+ * or graph branches - race on it; calls on one stream are ordered and safe.
+ */
+int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const void* sfa_dev, const void* b_dev,
+                                           const void* sfb_dev, const float* tensor_scale_a_dev,
+                                           const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
+                                           const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype,
+                                           int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * amax(|x|) / (448*6) computed in the input dtype and widened to float32, the per-tensor scale
  * TensorCoreNVFP4Layout.quantize derives when the caller gives none (comfy_kitchen/tensor/nvfp4.py:66-71).
  * scale_out_dev receives one float32.  Two launches on `stream` (reduce, finalise); no host sync.
