@@ -200,7 +200,7 @@ __device__ __forceinline__ bool elect_one() {
 //   high = (stride byte offset >> 4) | version 1 << 14 | layout << 29
 //   operands: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
 //   scale chunks: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart
-constexpr uint32_t LAYOUT_SWIZZLE_NONE = 0, LAYOUT_SWIZZLE_128B = 2;
+constexpr uint32_t LAYOUT_SWIZZLE_NONE = 0, LAYOUT_SWIZZLE_128B = 2, LAYOUT_SWIZZLE_64B = 4;
 constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout) { return (sbo_bytes >> 4) | (1u << 14) | (layout << 29); }
 constexpr uint32_t kOperandDescHi = desc_hi(1024, LAYOUT_SWIZZLE_128B);
 constexpr uint32_t kOperandDescLoFlags = (16u >> 4) << 16;
@@ -576,17 +576,29 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 //   * Epilogue warps of both CTAs report drained accumulators to CTA 0 with remote mbarrier arrives.
 // Scale chunks are fetched as 2-D tiles (a [chunks, 128 x u32] view of the tiled scale tensor, box of 4 chunks).
 
-constexpr int kStages2 = 5;
-constexpr int kA2 = BM * BK_BYTES;                 // 16 KiB: this CTA's 128 rows of A
-constexpr int kB2 = 128 * BK_BYTES;                // 16 KiB: this CTA's half of the 256 B rows
-constexpr int kSfa2 = CHUNKS * SF_CHUNK_BYTES;     // 2 KiB
-constexpr int kSfb2 = 2 * CHUNKS * SF_CHUNK_BYTES; // 4 KiB: both 128-row bands of the B tile
-constexpr int kStageBytes2 = kA2 + kB2 + kSfa2 + kSfb2;   // 38 KiB
-constexpr int kStagingBytes2 = 4 * 2 * STAGING_BYTES_PER_WARP;   // two staging tiles per epilogue warp
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + kStagingBytes2 + 1024 + 256;
+// KB = packed bytes of K per stage and row: 128 (256 elements, 128-byte swizzle, 5 stages of 38 KiB) or 64
+// (128 elements, 64-byte swizzle, 11 stages of 19 KiB).  The finer stages keep more bytes in flight for the same
+// shared memory (10 of 11 stages instead of 4 of 5 while one is being consumed), which hides more load latency.
+template <int KB>
+struct PairCfg {
+    static_assert(KB == 128 || KB == 64, "stage width");
+    static constexpr int kChunks = KB / 32;                         // 64-element MMA steps per stage
+    static constexpr int kA = BM * KB;                              // this CTA's 128 rows of A
+    static constexpr int kB = 128 * KB;                             // this CTA's half of the 256 B rows
+    static constexpr int kSfa = kChunks * SF_CHUNK_BYTES;
+    static constexpr int kSfb = 2 * kChunks * SF_CHUNK_BYTES;       // both 128-row bands of the B tile
+    static constexpr int kStageBytes = kA + kB + kSfa + kSfb;       // 38 KiB or 19 KiB
+    static constexpr int kStagingBytes = 4 * 2 * STAGING_BYTES_PER_WARP;   // two staging tiles per epilogue warp
+    static constexpr int kStages = (232448 - 1024 - 256 - kStagingBytes) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+    static constexpr uint32_t kLayout = (KB == 128) ? LAYOUT_SWIZZLE_128B : LAYOUT_SWIZZLE_64B;
+    static constexpr uint32_t kDescHi = desc_hi(8 * KB, kLayout);   // 8-row groups are 8 * KB bytes apart
+    static_assert(kStageBytes % 1024 == 0, "stages stay 1024-byte aligned");
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+    static_assert(2 * kStages + 5 <= 32, "barriers fit their 256 bytes");
+};
 constexpr int kAccCol1_2 = 192, kSfCol0_2 = 448, kSfRegion2 = 24;   // tensor-memory plan of the BN = 256 kernel
 constexpr uint32_t kIdesc2 = (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
-static_assert(kSmemBytes2 <= 232448, "shared memory budget");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -629,15 +641,18 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
         : "memory");
 }
 
-template <bool DBG>
+template <int KB, bool DBG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                        const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
+    using P = PairCfg<KB>;
+    constexpr int kStages2 = P::kStages, kStageBytes2 = P::kStageBytes, kA2 = P::kA, kB2 = P::kB, kSfa2 = P::kSfa;
+    constexpr int kChunks = P::kChunks;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = smem + kStages2 * kStageBytes2;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kStagingBytes2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + P::kStagingBytes);
     uint64_t* full_bar = bars;                       // [kStages2] used in CTA 0: loads of both CTAs -> MMA
     uint64_t* empty_bar = bars + kStages2;           // [kStages2] in each CTA: MMA -> this CTA's producer
     uint64_t* acc_full_bar = bars + 2 * kStages2;    // [2] in each CTA: MMA -> this CTA's epilogue
@@ -676,6 +691,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const uint32_t tmem_base = *tmem_slot;
 
     const int total_tiles = g.m_tiles * g.n_tiles;   // 256 x 256 tiles
+    const int k_stages = (g.sf_cbg + kChunks - 1) / kChunks;   // stages per tile
     auto now = [] { return DBG ? clock64() : 0ll; };
 
     if (warp == 0) {
@@ -693,7 +709,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int b_row = tn * 256 + (int)rank * 128;                // this CTA's half of the B tile
             const int sfa_chunk0 = (tm * 2 + (int)rank) * g.sf_cbg;
             const int sfb_chunk0 = tn * 2 * g.sf_cbg;
-            for (int kb = 0; kb < g.k_iters; ++kb) {
+            for (int kb = 0; kb < k_stages; ++kb) {
                 const long long t0 = now();
                 ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
@@ -703,11 +719,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const uint32_t bar = full0 + stage * 8;
                 if (elect_one()) {
                     mbar_expect_tx_cluster(bar, kStageBytes2);   // every box is transferred in full (zero fill past the ends)
-                    tma_load_2d_pair(st, &tmap_a, kb * BK_BYTES, a_row, bar);
-                    tma_load_2d_pair(st + kA2, &tmap_b, kb * BK_BYTES, b_row, bar);
-                    tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * CHUNKS, bar);
-                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * CHUNKS, bar);
-                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * CHUNKS, bar);
+                    tma_load_2d_pair(st, &tmap_a, kb * KB, a_row, bar);
+                    tma_load_2d_pair(st + kA2, &tmap_b, kb * KB, b_row, bar);
+                    tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * kChunks, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * kChunks, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * kChunks, bar);
                 }
                 __syncwarp();
                 if (++stage == kStages2) { stage = 0; phase ^= 1; }
@@ -737,7 +753,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * kAccCol1_2;
-            for (int kb = 0; kb < g.k_iters; ++kb) {
+            for (int kb = 0; kb < k_stages; ++kb) {
                 t0 = now();
                 ok = mbar_wait(smem_u32(&full_bar[0]) + stage * 8, phase, abort_flag, WAIT_STAGE_FULL);
                 ok = __all_sync(0xffffffffu, ok);
@@ -749,25 +765,30 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const uint32_t b_lo = a_lo + (kA2 >> 4);
                 const uint32_t sfa_lo = st_enc + ((kA2 + kB2) >> 4);
                 const uint32_t sfb_lo = sfa_lo + (kSfa2 >> 4);
-                const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                const int nchunk = min(kChunks, g.sf_cbg - kb * kChunks);
+                // scale factors of 64-element step j of the tile go to region (j/2) % 2: two alternating regions,
+                // each holding two steps
+                const int region0 = (kChunks == 2) ? (kb & 1) : 0;
                 if (elect_one()) {
 #pragma unroll
-                    for (int j = 0; j < CHUNKS; ++j) {
+                    for (int j = 0; j < kChunks; ++j) {
                         if (j < nchunk) {
-                            const uint32_t sfa_t = sf_t0 + (j >> 1) * kSfRegion2 + (j & 1) * 4;
-                            const uint32_t sfb_t = sf_t0 + (j >> 1) * kSfRegion2 + 8 + (j & 1) * 8;
+                            const uint32_t sf_r = sf_t0 + (region0 + (j >> 1)) * kSfRegion2;
+                            const uint32_t sfa_t = sf_r + (j & 1) * 4;
+                            const uint32_t sfb_t = sf_r + 8 + (j & 1) * 8;
                             tc_cp_sf_pair(sfa_t, desc64(sfa_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
                             tc_cp_sf_pair(sfb_t, desc64(sfb_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
                             tc_cp_sf_pair(sfb_t + 4, desc64(sfb_lo + (kSfa2 + j * SF_CHUNK_BYTES) / 16, kSfDescHi));
                         }
                     }
 #pragma unroll
-                    for (int j = 0; j < CHUNKS; ++j) {
+                    for (int j = 0; j < kChunks; ++j) {
                         if (j < nchunk) {
-                            const uint32_t sfa_t = sf_t0 + (j >> 1) * kSfRegion2 + (j & 1) * 4;
-                            const uint32_t sfb_t = sf_t0 + (j >> 1) * kSfRegion2 + 8 + (j & 1) * 8;
-                            tc_mma_pair(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
-                                        kIdesc2, sfa_t, sfb_t, (j != 0 || kb != 0) ? 1u : 0u);
+                            const uint32_t sf_r = sf_t0 + (region0 + (j >> 1)) * kSfRegion2;
+                            const uint32_t sfa_t = sf_r + (j & 1) * 4;
+                            const uint32_t sfb_t = sf_r + 8 + (j & 1) * 8;
+                            tc_mma_pair(d_tmem, desc64(a_lo + 2 * j, P::kDescHi), desc64(b_lo + 2 * j, P::kDescHi), kIdesc2,
+                                        sfa_t, sfb_t, (j != 0 || kb != 0) ? 1u : 0u);
                         }
                     }
                     tc_commit_pair(smem_u32(&empty_bar[0]) + stage * 8);   // this CTA's producer
@@ -797,7 +818,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         long long wait_acc = 0;
         const long long t_begin = now();
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
-        uint8_t* my_staging = staging + quad * 2 * STAGING_BYTES_PER_WARP;
+        uint8_t* my_staging = staging + quad * 2 * STAGING_BYTES_PER_WARP;   // two tiles per warp
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         const uint32_t overlap0 = map_to_cta(smem_u32(overlap_bar), 0);
         constexpr int kSteps = 256 / EPI_COLS;
@@ -939,16 +960,17 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // Packed operand [rows, k_bytes] row-major, boxes of 128 bytes x box_rows rows, 128-byte swizzle, zero fill.
-int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_bytes, int box_rows) {
+int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_bytes, int box_rows,
+                     int box_bytes = BK_BYTES) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)k_bytes, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)k_bytes};
-    cuuint32_t box[2] = {(cuuint32_t)BK_BYTES, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled (operand) failed with CUresult %d", (int)r);
     return CK_B200_OK;
@@ -969,13 +991,13 @@ int make_output_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N) {
     return CK_B200_OK;
 }
 
-// Tiled scale tensor seen as [chunks, 128 x u32] (one 512-byte chunk per row), boxes of 4 chunks, no swizzle.
-int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks) {
+// Tiled scale tensor seen as [chunks, 128 x u32] (one 512-byte chunk per row), boxes of box_chunks chunks, no swizzle.
+int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks, int box_chunks) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {128, (cuuint64_t)chunks};
     cuuint64_t strides[1] = {(cuuint64_t)SF_CHUNK_BYTES};
-    cuuint32_t box[2] = {128, (cuuint32_t)CHUNKS};
+    cuuint32_t box[2] = {128, (cuuint32_t)box_chunks};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -986,14 +1008,16 @@ int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks) {
 }
 
 // Pairs of CTAs that can be resident at once (clusters of 2 need two free SMs of one GPC), cached per device.
+template <int KB>
 int max_active_pairs(int* out) {
+    constexpr int kSmemBytes2 = PairCfg<KB>::kSmemBytes;
     static std::mutex mu;
     static int cache[64] = {0};
     int dev = 0;
     CKB_CUDA_OK(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == 0) {
-        auto kernel = gemm_nvfp4_pair_kernel<false>;
+        auto kernel = gemm_nvfp4_pair_kernel<KB, false>;
         CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * 148);
@@ -1015,19 +1039,22 @@ int max_active_pairs(int* out) {
     return CK_B200_OK;
 }
 
+template <int KB>
 int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream) {
-    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<true> : gemm_nvfp4_pair_kernel<false>;
+    using P = PairCfg<KB>;
+    constexpr int kSmemBytes2 = P::kSmemBytes;
+    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true> : gemm_nvfp4_pair_kernel<KB, false>;
     int pairs = 0;
-    if (int rc = max_active_pairs(&pairs)) return rc;
+    if (int rc = max_active_pairs<KB>(&pairs)) return rc;
     cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
     if (attr_err != cudaSuccess)
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
                     cudaGetErrorString(attr_err));
     CUtensorMap ma, mb, msa, msb, mo;
-    if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM)) return rc;
-    if (int rc = make_operand_map(&mb, b, g.N, K / 2, 128)) return rc;
-    if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg)) return rc;
-    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg)) return rc;
+    if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM, KB)) return rc;
+    if (int rc = make_operand_map(&mb, b, g.N, K / 2, 128, KB)) return rc;
+    if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg, P::kChunks)) return rc;
+    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, P::kChunks)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
         if (int rc = make_output_map(&mo, g.out, g.M, g.N)) return rc;
@@ -1174,7 +1201,8 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     if (workspace_dev && ((uintptr_t)workspace_dev & 15))
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
     float* scratch = (float*)workspace_dev;
-    if (variant == 3 && M > 128) return launch_gemm_pair(a_dev, b_dev, g, K, s);
+    if (variant == 4 && M > 128) return launch_gemm_pair<64>(a_dev, b_dev, g, K, s);
+    if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
     // one tile row: 128-column tiles give the most work items, and split-K (with scratch) fills the remaining SMs
     return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);

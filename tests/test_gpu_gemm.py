@@ -22,7 +22,7 @@ def ckb():
     return m
 
 
-@pytest.fixture(params=[1, 2, 3], ids=["bn128", "bn256", "pair256"])
+@pytest.fixture(params=[1, 2, 3, 4], ids=["bn128", "bn256", "pair256", "pair256-k128"])
 def variant(request, ckb):
     prev = ckb.set_tuning(1, request.param)
     yield request.param
