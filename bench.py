@@ -359,6 +359,27 @@ def run_ours(args, wl):
         "per_linear": per_linear,
     }
 
+    # ---- bandwidth sweep of the quantizer / dequantizer (BASELINE configuration 3 shapes), rank 0 only ----
+    sweep = None
+    if rank == 0 and not args.no_sweep:
+        sweep = []
+        for (sm, sk) in [(1024, 3072), (4096, 5120), (16384, 3072), (16384, 12288), (65536, 5120), (65536, 12288)]:
+            gx = torch.Generator(device=dev).manual_seed(sm + sk)
+            xx = torch.randn((sm, sk), generator=gx, device=dev, dtype=torch.bfloat16)
+            tt = ckb.dynamic_scale_nvfp4(xx)
+            qq, ss = ckb.quantize_nvfp4(xx, tt)
+            reps = 10
+            r_q, _ = graphed(lambda: ckb.quantize_nvfp4(xx, tt))
+            r_d, _ = graphed(lambda: ckb.dequantize_nvfp4(qq, tt, ss, torch.bfloat16))
+            t_q = timed(r_q, reps) / reps
+            t_d = timed(r_d, reps) / reps
+            nbytes = sm * sk * 2.5625
+            sweep.append({"M": sm, "K": sk, "quantize_us": t_q * 1e3, "quantize_gbs": nbytes / (t_q * 1e-3) / 1e9,
+                          "dequantize_us": t_d * 1e3, "dequantize_gbs": nbytes / (t_d * 1e-3) / 1e9})
+            del xx, qq, ss, r_q, r_d
+            graphs.clear()
+        torch.cuda.empty_cache()
+
     # ---- cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend ----
     try:
         from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
@@ -433,6 +454,7 @@ def run_ours(args, wl):
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "gemm_only_tflops": gemm_tflops,
+            "quantize_sweep": sweep,
         }
         print(json.dumps(line), flush=True)
     if distributed:
@@ -447,6 +469,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the quantizer bandwidth sweep")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]

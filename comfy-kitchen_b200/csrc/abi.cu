@@ -7,7 +7,7 @@
 namespace ckb {
 
 std::atomic<long long> g_launches{0};
-std::atomic<int> g_quant_variant{1};
+std::atomic<int> g_quant_variant{2};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
 

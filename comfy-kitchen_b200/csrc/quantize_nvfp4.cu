@@ -211,6 +211,21 @@ __device__ __forceinline__ bool quantize8_bracket(const float (&f)[8], float r, 
     return (word == pack8_e2m1_hi_first(e)) && (r != 0.0f);
 }
 
+// The same word with one division-free correctly rounded quotient per element: r = RN(1/t), q0 = x*r (within two
+// ulp), residual x - t*q0 by a fused multiply-add, q = q0 + residual*r (one round of Markstein's correction, which
+// yields RN(x/t) from a correctly rounded reciprocal).  The residual is rounded toward minus infinity: where it is
+// exact that changes nothing except that an exact zero comes out as -0, which lets the last step keep the sign of
+// a -0 input (-0 + -0 = -0, -0 + +0 = +0) without a separate sign fix-up.  Needs t in [2^-100, 2^100].
+__device__ __forceinline__ uint32_t quantize8_markstein(const float (&f)[8], float t, float r) {
+    float d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float q0 = __fmul_rn(f[i], r);
+        d[i] = __fmaf_rn(__fmaf_rd(-t, q0, f[i]), r, q0);
+    }
+    return pack8_e2m1_hi_first(d);
+}
+
 // ---- quantize -------------------------------------------------------------------------------------
 
 struct QuantArgs {
@@ -259,23 +274,35 @@ __device__ __forceinline__ void quantize_pair(const LaneCtx& c, const typename I
     const float amax = fmaxf(odd ? half_b : half_a, other_half);
     s8 = 0;
     float t = 0.0f, rcp = 0.0f;
-    if (VARIANT == 1) {
+    if (VARIANT != 0) {
         const bool fast = c.ts_in_range && amax >= 0x1p-60f && amax <= 0x1p60f;
         if (__all_sync(0xffffffffu, fast && mine_in)) {
             block_scale(amax, c.ts, c.rcp_ts, true, s8, t);
-            rcp = rcp_approx(t);
+            rcp = VARIANT == 2 ? __frcp_rn(t) : rcp_approx(t);
             // t is zero (block scale rounded to zero) or, never with these ranges, outside [2^-100, 2^100]: flag it
             if (!(t >= 0x1p-100f && t <= 0x1p100f)) rcp = 0.0f;
         } else if (mine_in) {
             block_scale(amax, c.ts, c.rcp_ts, fast, s8, t);
-            if (t >= 0x1p-100f && t <= 0x1p100f) rcp = rcp_approx(t);
+            // the residual form also needs finite elements (inf - inf otherwise): only blocks with amax in range
+            if (VARIANT == 2) { if (fast && t >= 0x1p-100f && t <= 0x1p100f) rcp = __frcp_rn(t); }
+            else if (t >= 0x1p-100f && t <= 0x1p100f) rcp = rcp_approx(t);
         }
     } else if (mine_in) {
         block_scale(amax, c.ts, 0.0f, false, s8, t);
     }
     const float t_other = __shfl_xor_sync(0xffffffffu, t, 1);
     const float t_a = odd ? t_other : t, t_b = odd ? t : t_other;
-    if (VARIANT == 1) {
+    if (VARIANT == 2) {
+        const float rcp_other = __shfl_xor_sync(0xffffffffu, rcp, 1);
+        const float rcp_a = odd ? rcp_other : rcp, rcp_b = odd ? rcp : rcp_other;
+        if (__all_sync(0xffffffffu, rcp_a != 0.0f && rcp_b != 0.0f)) {
+            word_a = quantize8_markstein(fa, t_a, rcp_a);
+            word_b = quantize8_markstein(fb, t_b, rcp_b);
+        } else {   // a decode scale that is zero or out of range
+            word_a = (rcp_a != 0.0f) ? quantize8_markstein(fa, t_a, rcp_a) : quantize8_exact(fa, t_a);
+            word_b = (rcp_b != 0.0f) ? quantize8_markstein(fb, t_b, rcp_b) : quantize8_exact(fb, t_b);
+        }
+    } else if (VARIANT == 1) {
         const float rcp_other = __shfl_xor_sync(0xffffffffu, rcp, 1);
         const float rcp_a = odd ? rcp_other : rcp, rcp_b = odd ? rcp : rcp_other;
         const bool ok_a = quantize8_bracket(fa, rcp_a, word_a);
@@ -440,7 +467,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(
     c.odd = c.sub & 1;
     c.ts = __ldg(a.pts);
     c.ts_in_range = c.ts >= 0x1p-60f && c.ts <= 0x1p60f;
-    c.rcp_ts = (VARIANT == 1 && c.ts_in_range) ? __frcp_rn(c.ts) : 0.0f;
+    c.rcp_ts = (VARIANT != 0 && c.ts_in_range) ? __frcp_rn(c.ts) : 0.0f;
     c.row_in = r < a.rows;
     c.row_out = r < a.prow;
     c.hi_first = a.hi_first != 0;
@@ -493,9 +520,11 @@ int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t st
               (unsigned)ceil_div64(gy_total, 65535));
     if (vec) {
         if (variant == 0) quantize_nvfp4_kernel<DT, true, 0><<<grid, block, 0, stream>>>(a);
+        else if (variant == 2) quantize_nvfp4_kernel<DT, true, 2><<<grid, block, 0, stream>>>(a);
         else quantize_nvfp4_kernel<DT, true, 1><<<grid, block, 0, stream>>>(a);
     } else {
         if (variant == 0) quantize_nvfp4_kernel<DT, false, 0><<<grid, block, 0, stream>>>(a);
+        else if (variant == 2) quantize_nvfp4_kernel<DT, false, 2><<<grid, block, 0, stream>>>(a);
         else quantize_nvfp4_kernel<DT, false, 1><<<grid, block, 0, stream>>>(a);
     }
     g_launches.fetch_add(1);
@@ -639,7 +668,7 @@ extern "C" int ck_b200_quantize_nvfp4(const void* x_dev, int x_dtype, const floa
     if (((uintptr_t)q_out_dev & 3) || ((uintptr_t)sf_out_dev & 3))
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4: outputs must be 4-byte aligned");
     const bool vec = (cols % 8 == 0) && (((uintptr_t)x_dev & 15) == 0);
-    const int variant = g_quant_variant.load() ? 1 : 0;
+    const int variant = g_quant_variant.load();
     cudaStream_t s = (cudaStream_t)stream;
     switch (x_dtype) {
         case CK_B200_DTYPE_F32: return launch_quantize<CK_B200_DTYPE_F32>(a, vec, variant, sms, s);

@@ -134,7 +134,7 @@ int ck_b200_read_device_status(int* status_out);
 /* Tuning switches used by tests and benchmarks to select kernel variants: key/value integers,
  * returns the previous value or -1 for an unknown key.  No counterpart in the reference (its
  * environment switches, comfy_kitchen/backends/cuda/__init__.py:212-215, do not touch this path). */
-#define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions everywhere, 1 = shared-reciprocal exact division (default) */
+#define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions, 1 = reciprocal bracket + exact fallback, 2 = one-round residual correction (default) */
 #define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic */
 #define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the GEMM kernel's first CTA prints the cycles its roles spent waiting */
 int ck_b200_set_tuning(int key, int value);

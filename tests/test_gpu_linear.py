@@ -1,0 +1,55 @@
+"""NVFP4Linear on the GPU: state-dict round trip in the reference checkpoint format and forward parity with the
+CPU oracle (quantize with the layout's dynamic scale, dequantize -> fp32 matmul)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import from_bits, seeded_randn, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 512), (49, 200, 96), (3, 1024, 2048)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("static_input_scale", [False, True])
+def test_linear_forward_matches_oracle(shape, static_input_scale, oracle):
+    import comfy_kitchen_b200 as ckb
+    M, N, K = shape
+    w = seeded_randn((N, K), seed=1, std=0.02).cuda()
+    b = seeded_randn((1, N), seed=2, std=0.1).reshape(N).cuda()
+    x = seeded_randn((2, M, K), seed=3).cuda()           # leading batch dimension
+    inp = torch.tensor(0.0123, dtype=torch.float32) if static_input_scale else None
+    lin = ckb.NVFP4Linear.from_float(w, b, input_scale=inp)
+    y = lin(x)
+    assert tuple(y.shape) == (2, M, N) and y.dtype == torch.bfloat16
+
+    x2 = x.reshape(-1, K).cpu()
+    ts_w = oracle.dynamic_scale(to_bits(w), 2)
+    ts_x = float(np.float32(0.0123)) if static_input_scale else oracle.dynamic_scale(to_bits(x2), 2)
+    assert np.float32(ts_w) == np.float32(lin.weight_scale_2.item())
+    qw, sfw = oracle.quantize_nvfp4(to_bits(w), 2, ts_w, pad_16x=True)
+    qx, sfx = oracle.quantize_nvfp4(to_bits(x2), 2, ts_x, pad_16x=True)
+    assert np.array_equal(qw, lin.weight.cpu().numpy()) and np.array_equal(sfw, lin.weight_scale.cpu().numpy())
+    bias_p = np.zeros(qw.shape[0], np.uint16)
+    bias_p[:N] = to_bits(b)
+    ref = from_bits(oracle.scaled_mm_nvfp4(qx, qw, ts_x, ts_w, sfx, sfw, bias=bias_p), 2).float()[: 2 * M, :N]
+    got = y.reshape(-1, N).cpu().float()
+    rel = float((got - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
+    assert rel <= 1e-2
+
+
+def test_linear_state_dict_round_trip():
+    import comfy_kitchen_b200 as ckb
+    w = seeded_randn((128, 256), seed=5, std=0.02).cuda()
+    lin = ckb.NVFP4Linear.from_float(w, None, input_scale=torch.tensor(0.02))
+    sd = lin.state_dict()
+    assert set(sd) == {"weight", "weight_scale", "weight_scale_2", "input_scale"}
+    assert sd["weight"].dtype == torch.uint8 and sd["weight_scale"].dtype == torch.uint8
+    # the reference sample stores the block scales flat
+    sd = {k: v.clone() for k, v in sd.items()}
+    sd["weight_scale"] = sd["weight_scale"].reshape(-1)
+    other = ckb.NVFP4Linear(256, 128, bias=False, device="cuda")
+    other.load_state_dict(sd)
+    x = seeded_randn((32, 256), seed=6).cuda()
+    assert torch.equal(lin(x), other(x))

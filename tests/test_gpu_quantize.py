@@ -19,7 +19,7 @@ def ckb():
     return m
 
 
-@pytest.fixture(params=[1, 0], ids=["shared-reciprocal", "ieee-div"])
+@pytest.fixture(params=[1, 2, 0], ids=["bracket", "residual", "ieee-div"])
 def variant(request, ckb):
     prev = ckb.set_tuning(0, request.param)
     yield request.param
@@ -128,6 +128,23 @@ def test_extreme_magnitudes(ckb, oracle, variant):
         q, sf = ckb.quantize_nvfp4(_dev(x), _dev(tsd))
         q_ref, sf_ref = oracle.quantize_nvfp4(to_bits(x), 0, float(tsd))
         assert np.array_equal(to_bits(sf), sf_ref) and np.array_equal(to_bits(q), q_ref)
+
+
+def test_infinite_elements(ckb, oracle, variant):
+    """Blocks holding +-inf: the block scale clamps at 448 and the infinite elements saturate to +-6."""
+    g = torch.Generator().manual_seed(8)
+    base = torch.randn(32, 128, generator=g)
+    base[3, 5] = float("inf")
+    base[3, 40] = float("-inf")
+    base[17, 127] = float("-inf")
+    base[20, 64:80] = float("inf")
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        x = base.to(dtype)
+        for ts in (2.0 ** -7, 0.0123):
+            tsd = torch.tensor(ts, dtype=torch.float32)
+            q, sf = ckb.quantize_nvfp4(_dev(x), _dev(tsd))
+            q_ref, sf_ref = oracle.quantize_nvfp4(to_bits(x), CODE[dtype], float(tsd))
+            assert np.array_equal(to_bits(sf), sf_ref) and np.array_equal(to_bits(q), q_ref)
 
 
 def test_scale_tensor_padding_is_written(ckb):
