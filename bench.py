@@ -214,6 +214,8 @@ def run_ours(args, wl):
         raise SystemExit("bench.py needs a CUDA device: comfy_kitchen_b200 has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.no_dependent_launch:
+        ckb.set_tuning(3, 0)
     distributed = world > 1
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -470,6 +472,8 @@ def main():
     ap.add_argument("--workload", default="flux", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantizer bandwidth sweep")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="launch kernels fully serialised instead of with programmatic stream serialisation")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]

@@ -8,6 +8,7 @@ namespace ckb {
 
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_quant_variant{2};
+std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
 
@@ -87,6 +88,7 @@ int64_t ck_b200_query(int what) {
 int ck_b200_set_tuning(int key, int value) {
     switch (key) {
         case CK_B200_TUNE_QUANT_VARIANT: return ckb::g_quant_variant.exchange(value);
+        case CK_B200_TUNE_DEPENDENT_LAUNCH: return ckb::g_dependent_launch.exchange(value);
         case CK_B200_TUNE_GEMM_VARIANT: return ckb::g_gemm_variant.exchange(value);
         case CK_B200_TUNE_GEMM_DEBUG: return ckb::g_gemm_debug.exchange(value);
         default: return -1;

@@ -23,6 +23,7 @@ extern std::atomic<long long> g_launches;
 extern std::atomic<int> g_quant_variant;
 extern std::atomic<int> g_gemm_variant;
 extern std::atomic<int> g_gemm_debug;
+extern std::atomic<int> g_dependent_launch;
 
 // Checks that the current device is compute capability 10.x (cached per device ordinal).
 int check_device(int* sm_count_out);
@@ -40,6 +41,32 @@ static inline int64_t ceil_div64(int64_t x, int64_t m) { return (x + m - 1) / m;
 // ---- device side ------------------------------------------------------------------------------
 
 #ifdef __CUDACC__
+
+// Launch with programmatic stream serialisation: the grid may be scheduled while the previous kernel on the
+// stream is still draining, and runs its prologue up to grid_dependency_wait() before that kernel has finished.
+// Every kernel launched through here calls allow_dependent_launch() first thing and grid_dependency_wait() before
+// its first access to global memory, so ordering and visibility are those of a plain in-stream launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_dependent_launch.load() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The next kernel on the stream may start being scheduled (it still waits for this grid to finish and flush
+// before it touches memory).
+__device__ __forceinline__ void allow_dependent_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Returns once every kernel this grid depends on has completed and its writes are visible.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

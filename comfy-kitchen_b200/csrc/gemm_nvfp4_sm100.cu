@@ -298,6 +298,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    allow_dependent_launch();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -322,6 +323,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();   // barriers and tensor memory are set up while the previous kernel drains
 
     const int total_items = g.m_tiles * g.n_tiles * g.splits;
     // cycle counters of the debug build (DBG): compiled out otherwise
@@ -665,6 +667,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    allow_dependent_launch();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) {
@@ -689,6 +692,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     cluster_sync_all();   // barriers of both CTAs are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();   // barriers and tensor memory are set up while the previous kernel drains
 
     const int total_tiles = g.m_tiles * g.n_tiles;   // 256 x 256 tiles
     const int k_stages = (g.sf_cbg + kChunks - 1) / kChunks;   // stages per tile
@@ -915,9 +919,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                                             const float* tsa, const float* tsb, const float* alpha_ptr,
                                                             const void* bias, int bias_dtype, void* out, int out_dtype) {
+    allow_dependent_launch();
     const int64_t quads = (int64_t)M * N / 4;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= quads) return;
+    grid_dependency_wait();
     const float alpha = alpha_ptr ? __ldg(alpha_ptr) : __fmul_rn(__ldg(tsa), __ldg(tsb));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < splits; ++s) {
@@ -1072,9 +1078,9 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     g.partial = nullptr;
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
-    kernel<<<grid, NUM_THREADS, kSmemBytes2, stream>>>(ma, mb, msa, msb, mo, g);
+    const cudaError_t err = launch_dependent(kernel, dim3(grid), dim3(NUM_THREADS), kSmemBytes2, stream, ma, mb, msa, msb, mo, g);
     g_launches.fetch_add(1);
-    CKB_CUDA_OK(cudaGetLastError());
+    CKB_CUDA_OK(err);
     return CK_B200_OK;
 }
 
@@ -1127,15 +1133,16 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     }
     const int64_t items = (int64_t)g.m_tiles * g.n_tiles * g.splits;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    kernel<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mb, mo, g);
+    const cudaError_t err = launch_dependent(kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
     g_launches.fetch_add(1);
-    CKB_CUDA_OK(cudaGetLastError());
+    CKB_CUDA_OK(err);
     if (g.splits > 1) {
         const int64_t quads = (int64_t)g.M * g.N / 4;
-        splitk_reduce_kernel<<<(unsigned)ceil_div64(quads, 256), 256, 0, stream>>>(
-            g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias, g.bias_dtype, g.out, g.out_dtype);
+        const cudaError_t err2 = launch_dependent(splitk_reduce_kernel, dim3((unsigned)ceil_div64(quads, 256)), dim3(256), 0,
+                                                  stream, g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias,
+                                                  g.bias_dtype, g.out, g.out_dtype);
         g_launches.fetch_add(1);
-        CKB_CUDA_OK(cudaGetLastError());
+        CKB_CUDA_OK(err2);
     }
     return CK_B200_OK;
 }

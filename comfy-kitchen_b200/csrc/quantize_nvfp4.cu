@@ -452,6 +452,7 @@ __device__ __forceinline__ void walk_edge(const LaneCtx& c, int u_begin, int u_e
 template <int DT, bool VEC, int VARIANT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(const QuantArgs a) {
     using In = Input<DT>;
+    allow_dependent_launch();
     const int lane = threadIdx.x;
     const int seg = blockIdx.x * blockDim.y + threadIdx.y;
     const int group = (blockIdx.z * 65535 + blockIdx.y) * blockDim.z + threadIdx.z;
@@ -465,6 +466,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(
     LaneCtx c;
     c.sub = lane & 7;
     c.odd = c.sub & 1;
+    grid_dependency_wait();
     c.ts = __ldg(a.pts);
     c.ts_in_range = c.ts >= 0x1p-60f && c.ts <= 0x1p60f;
     c.rcp_ts = (VARIANT != 0 && c.ts_in_range) ? __frcp_rn(c.ts) : 0.0f;
@@ -518,17 +520,18 @@ int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t st
     dim3 block(32, wx, wy);
     dim3 grid((unsigned)ceil_div64(a.segments, wx), (unsigned)(gy_total < 65535 ? gy_total : 65535),
               (unsigned)ceil_div64(gy_total, 65535));
+    cudaError_t err;
     if (vec) {
-        if (variant == 0) quantize_nvfp4_kernel<DT, true, 0><<<grid, block, 0, stream>>>(a);
-        else if (variant == 2) quantize_nvfp4_kernel<DT, true, 2><<<grid, block, 0, stream>>>(a);
-        else quantize_nvfp4_kernel<DT, true, 1><<<grid, block, 0, stream>>>(a);
+        if (variant == 0) err = launch_dependent(quantize_nvfp4_kernel<DT, true, 0>, grid, block, 0, stream, a);
+        else if (variant == 2) err = launch_dependent(quantize_nvfp4_kernel<DT, true, 2>, grid, block, 0, stream, a);
+        else err = launch_dependent(quantize_nvfp4_kernel<DT, true, 1>, grid, block, 0, stream, a);
     } else {
-        if (variant == 0) quantize_nvfp4_kernel<DT, false, 0><<<grid, block, 0, stream>>>(a);
-        else if (variant == 2) quantize_nvfp4_kernel<DT, false, 2><<<grid, block, 0, stream>>>(a);
-        else quantize_nvfp4_kernel<DT, false, 1><<<grid, block, 0, stream>>>(a);
+        if (variant == 0) err = launch_dependent(quantize_nvfp4_kernel<DT, false, 0>, grid, block, 0, stream, a);
+        else if (variant == 2) err = launch_dependent(quantize_nvfp4_kernel<DT, false, 2>, grid, block, 0, stream, a);
+        else err = launch_dependent(quantize_nvfp4_kernel<DT, false, 1>, grid, block, 0, stream, a);
     }
     g_launches.fetch_add(1);
-    CKB_CUDA_OK(cudaGetLastError());
+    CKB_CUDA_OK(err);
     return CK_B200_OK;
 }
 
@@ -583,8 +586,10 @@ __global__ void __launch_bounds__(256) dequantize_nvfp4_kernel(const uint8_t* __
                                                                int64_t rows, int64_t words_per_row, int sf_cbg,
                                                                int hi_first) {
     using Out = Output<DT>;
+    allow_dependent_launch();
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= rows * words_per_row) return;
+    grid_dependency_wait();
     const int64_t r = gid / words_per_row;
     const int64_t h = gid % words_per_row;
     uint32_t w = ldg_stream4(q + gid * 4);
@@ -700,19 +705,20 @@ extern "C" int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tens
     const uint8_t* q = (const uint8_t*)q_dev;
     const uint8_t* sf = (const uint8_t*)sf_dev;
     const int hf = hi_first ? 1 : 0;
+    cudaError_t err;
     switch (out_dtype) {
         case CK_B200_DTYPE_F32:
-            dequantize_nvfp4_kernel<CK_B200_DTYPE_F32><<<(unsigned)blocks, 256, 0, s>>>(q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_F32>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
         case CK_B200_DTYPE_F16:
-            dequantize_nvfp4_kernel<CK_B200_DTYPE_F16><<<(unsigned)blocks, 256, 0, s>>>(q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_F16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
         default:
-            dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16><<<(unsigned)blocks, 256, 0, s>>>(q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
     }
     g_launches.fetch_add(1);
-    CKB_CUDA_OK(cudaGetLastError());
+    CKB_CUDA_OK(err);
     return CK_B200_OK;
 }
 

@@ -137,6 +137,8 @@ int ck_b200_read_device_status(int* status_out);
 #define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions, 1 = reciprocal bracket + exact fallback, 2 = one-round residual correction (default) */
 #define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic */
 #define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the GEMM kernel's first CTA prints the cycles its roles spent waiting */
+#define CK_B200_TUNE_DEPENDENT_LAUNCH 3 /* non-zero (default): kernels are launched with programmatic stream
+                                          serialisation, so a kernel's set-up overlaps the previous kernel's tail */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus
