@@ -361,9 +361,10 @@ def run_ours(args, wl):
         "per_linear": per_linear,
     }
 
-    # ---- bandwidth sweep of the quantizer / dequantizer (BASELINE configuration 3 shapes), rank 0 only ----
+    # ---- bandwidth sweep of the quantizer / dequantizer (BASELINE configuration 3 shapes), single-GPU runs only:
+    # timed() synchronises all ranks, so every rank would have to run it ----
     sweep = None
-    if rank == 0 and not args.no_sweep:
+    if not distributed and not args.no_sweep:
         sweep = []
         for (sm, sk) in [(1024, 3072), (4096, 5120), (16384, 3072), (16384, 12288), (65536, 5120), (65536, 12288)]:
             gx = torch.Generator(device=dev).manual_seed(sm + sk)
