@@ -14,9 +14,9 @@ from .build import build_library
 from .ops import (dequantize_nvfp4, dynamic_scale_nvfp4, launches, quantize_nvfp4, read_device_status,
                   scaled_mm_nvfp4, set_tuning)
 from .linear import NVFP4Linear
-from .sharded import ShardedNVFP4Linear, shard_rows
+from .sharded import PeerGroup, PeerMemory, ShardedNVFP4Linear, shard_rows
 
 __all__ = [
     "quantize_nvfp4", "dequantize_nvfp4", "scaled_mm_nvfp4", "dynamic_scale_nvfp4", "install", "uninstall",
-    "build_library", "NVFP4Linear", "ShardedNVFP4Linear", "shard_rows", "set_tuning", "launches", "read_device_status",
+    "build_library", "NVFP4Linear", "PeerGroup", "PeerMemory", "ShardedNVFP4Linear", "shard_rows", "set_tuning", "launches", "read_device_status",
 ]

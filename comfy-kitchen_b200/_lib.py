@@ -16,6 +16,12 @@ EXPORTED_SYMBOLS = (
     "ck_b200_dequantize_nvfp4",
     "ck_b200_scaled_mm_nvfp4",
     "ck_b200_scaled_mm_nvfp4_static_scratch",
+    "ck_b200_scaled_mm_nvfp4_all_gather",
+    "ck_b200_peer_barrier",
+    "ck_b200_peer_alloc",
+    "ck_b200_peer_open",
+    "ck_b200_peer_close",
+    "ck_b200_peer_free",
     "ck_b200_dynamic_scale_nvfp4",
     "ck_b200_last_error",
     "ck_b200_query",
@@ -50,6 +56,19 @@ def load() -> ctypes.CDLL:
     L.ck_b200_scaled_mm_nvfp4.restype = i32
     L.ck_b200_scaled_mm_nvfp4_static_scratch.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i64, i64, i64, vp]
     L.ck_b200_scaled_mm_nvfp4_static_scratch.restype = i32
+    L.ck_b200_scaled_mm_nvfp4_all_gather.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, ctypes.POINTER(vp), i32, i32, i32,
+                                                     i64, i64, i64, vp]
+    L.ck_b200_scaled_mm_nvfp4_all_gather.restype = i32
+    L.ck_b200_peer_barrier.argtypes = [ctypes.POINTER(vp), i32, i32, vp, vp]
+    L.ck_b200_peer_barrier.restype = i32
+    L.ck_b200_peer_alloc.argtypes = [sz, ctypes.POINTER(vp), vp]
+    L.ck_b200_peer_alloc.restype = i32
+    L.ck_b200_peer_open.argtypes = [vp, ctypes.POINTER(vp)]
+    L.ck_b200_peer_open.restype = i32
+    L.ck_b200_peer_close.argtypes = [vp]
+    L.ck_b200_peer_close.restype = i32
+    L.ck_b200_peer_free.argtypes = [vp]
+    L.ck_b200_peer_free.restype = i32
     L.ck_b200_dynamic_scale_nvfp4.argtypes = [vp, i32, i64, vp, vp]
     L.ck_b200_dynamic_scale_nvfp4.restype = i32
     L.ck_b200_last_error.argtypes = []

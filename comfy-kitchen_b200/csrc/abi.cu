@@ -95,4 +95,49 @@ int ck_b200_set_tuning(int key, int value) {
     }
 }
 
+// ---- memory that the other ranks of a node can address (CUDA IPC) --------------------------------------------
+
+int ck_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out) {
+    if (int rc = ckb::check_device(nullptr)) return rc;
+    if (!ptr_out || !handle_out || bytes == 0)
+        return ckb::fail(CK_B200_ERR_INVALID_ARGUMENT, "peer_alloc: null pointer or zero size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == CK_B200_PEER_HANDLE_BYTES, "handle size");
+    void* p = nullptr;
+    CKB_CUDA_OK(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return ckb::fail(CK_B200_ERR_CUDA, "peer_alloc: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return CK_B200_OK;
+}
+
+int ck_b200_peer_open(const void* handle, void** ptr_out) {
+    if (int rc = ckb::check_device(nullptr)) return rc;
+    if (!handle || !ptr_out) return ckb::fail(CK_B200_ERR_INVALID_ARGUMENT, "peer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    CKB_CUDA_OK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr_out = p;
+    return CK_B200_OK;
+}
+
+int ck_b200_peer_close(void* ptr) {
+    if (!ptr) return CK_B200_OK;
+    CKB_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+    return CK_B200_OK;
+}
+
+int ck_b200_peer_free(void* ptr) {
+    if (!ptr) return CK_B200_OK;
+    CKB_CUDA_OK(cudaFree(ptr));
+    return CK_B200_OK;
+}
+
 }  // extern "C"

@@ -47,7 +47,8 @@ constexpr int EPI_COLS = 32;        // accumulator columns per epilogue step
 constexpr int STAGING_BYTES_PER_WARP = 32 * EPI_COLS * 2;   // 32 rows x 32 sixteen-bit outputs
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // about 1.5 s
 
-enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5 };
+enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5,
+                WAIT_PEER_BARRIER = 6 };
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -69,6 +70,11 @@ struct GemmArgs {
     float* partial;       // [splits, M, N] fp32 scratch (split-K only)
     int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
     int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
+    // fused all-gather (CTA-pair kernel, 16-bit output): `out` is this rank's column block inside its own
+    // [M, ld_out] matrix and every staged tile is also stored to the same block of the other ranks' matrices
+    int64_t ld_out;       // row stride of the output matrix in elements (N for a plain GEMM)
+    int n_peers;
+    uint8_t* peer_out[7]; // origin of the column block in each peer's matrix, as mapped into this process
 };
 
 template <int BN>
@@ -242,6 +248,10 @@ __device__ __forceinline__ uint32_t pack16(float a, float b, int out_dtype) {
 
 // Direct global stores of 32 consecutive outputs of one row (n0 % 32 == 0; N % 8 == 0 so groups of 8 columns are
 // either fully inside or fully outside).
+__device__ __forceinline__ void st_global_v4(void* p, const uint4& v) {
+    asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 __device__ __forceinline__ void store_row32(const GemmArgs& g, int64_t row, int n0, const float (&y)[32]) {
     if (g.out_dtype == CK_B200_DTYPE_F32) {
         float* p = (float*)g.out + row * g.N + n0;
@@ -865,6 +875,21 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         tma_store_2d(&tmap_out, n0, row0, smem_u32(tile_smem));
                         tma_store_commit();
                     }
+                    if (g.n_peers > 0) {
+                        // the same tile to the other ranks: rows as 64-byte segments, four lanes per row and eight
+                        // rows per store instruction, read back from the staged (swizzled) tile
+                        const int c = lane & 3;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int r = (lane >> 2) + 8 * j;
+                            const uint4 o = *reinterpret_cast<const uint4*>(tile_smem + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+                            if (row0 + r < g.M && n0 + c * 8 < g.N) {
+                                const int64_t off = ((int64_t)(row0 + r) * g.ld_out + n0 + c * 8) * 2;
+#pragma unroll 1
+                                for (int p = 0; p < g.n_peers; ++p) st_global_v4(g.peer_out[p] + off, o);
+                            }
+                        }
+                    }
                     buf ^= 1;
                 } else if (row < g.M && n0 < g.N) {
                     store_row32(g, row, n0, y);
@@ -911,6 +936,42 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
+}
+
+// ---- barrier between the ranks of one node (kernel) ---------------------------------------------------
+
+struct BarrierArgs {
+    uint32_t* flags[8];   // flags[r]: rank r's array of `world` counters (flags[rank] is local memory)
+    uint32_t* epoch;      // local: barriers completed so far
+    int world, rank;
+};
+
+// One block.  Thread t signals rank t (writes the new epoch into slot `rank` of its array) and waits until rank t
+// has signalled this rank.  The wait is bounded (two seconds): on expiry the kernel records WAIT_PEER_BARRIER in
+// the status word and returns, so a missing peer leaves the context usable.
+__global__ void peer_barrier_kernel(const BarrierArgs b) {
+    const int t = threadIdx.x;
+    const uint32_t target = *b.epoch + 1;
+    if (t < b.world && t != b.rank) {
+        __threadfence_system();   // this GPU's earlier stores to the peers are ordered before the signal
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(b.flags[t] + b.rank), "r"(target) : "memory");
+        const uint32_t* mine = b.flags[b.rank] + t;
+        unsigned long long t0, now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if ((int32_t)(v - target) >= 0) break;
+            __nanosleep(200);
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - t0 > 2000000000ull) {
+                atomicCAS(&g_device_status, 0, (int)WAIT_PEER_BARRIER);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (t == 0) *b.epoch = target;
 }
 
 // ---- split-K reduction ----------------------------------------------------------------------------
@@ -983,11 +1044,11 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_
 }
 
 // 16-bit output [M, N] row-major, boxes of 32 columns (64 bytes) x 32 rows, 64-byte swizzle.
-int make_output_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N) {
+int make_output_map(CUtensorMap* map, void* ptr, int64_t M, int64_t N, int64_t ld) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)EPI_COLS, 32};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1063,7 +1124,7 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, P::kChunks)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
-        if (int rc = make_output_map(&mo, g.out, g.M, g.N)) return rc;
+        if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
     } else {
         mo = ma;   // not used by the kernel
     }
@@ -1109,7 +1170,7 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     if (int rc = make_operand_map(&mb, b, g.N, K / 2, BN)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
-        if (int rc = make_output_map(&mo, g.out, g.M, g.N)) return rc;
+        if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
     } else {
         mo = ma;   // not used by the kernel
     }
@@ -1153,10 +1214,18 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
 using namespace ckb;
 
 namespace {
+// Where a fused all-gather sends the output besides `out_dev`: the column block's origin in every other rank's matrix.
+struct GatherSpec {
+    int64_t ld;
+    int n_peers;
+    uint8_t* peers[7];
+};
+
 int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
                    const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
                    const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N,
-                   int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream) {
+                   int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream,
+                   const GatherSpec* gather = nullptr) {
     int sms = 0;
     if (int rc = check_device(&sms)) return rc;
     if (!a_dev || !sfa_dev || !b_dev || !sfb_dev || !out_dev)
@@ -1199,6 +1268,9 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     g.partial = nullptr;
     g.raster_group = 1;
     g.tma_store = 0;
+    g.ld_out = N;
+    g.n_peers = 0;
+    for (int p = 0; p < 7; ++p) g.peer_out[p] = nullptr;
     g.debug = g_gemm_debug.load();
     int variant = g_gemm_variant.load();
     // CTA pairs with 256x256 tiles when the problem has more than one tile row and column; otherwise one CTA per
@@ -1208,6 +1280,15 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     if (workspace_dev && ((uintptr_t)workspace_dev & 15))
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
     float* scratch = (float*)workspace_dev;
+    if (gather) {
+        if (out_dtype == CK_B200_DTYPE_F32 || M <= 128 || N <= 128)
+            return fail(CK_B200_ERR_INVALID_ARGUMENT,
+                        "scaled_mm_nvfp4_all_gather: needs a 16-bit output, M > 128 and more than 128 local columns");
+        g.ld_out = gather->ld;
+        g.n_peers = gather->n_peers;
+        for (int p = 0; p < gather->n_peers; ++p) g.peer_out[p] = gather->peers[p];
+        return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
+    }
     if (variant == 4 && M > 128) return launch_gemm_pair<64>(a_dev, b_dev, g, K, s);
     if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
@@ -1225,6 +1306,54 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
                           bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, workspace_dev, workspace_bytes, stream);
 }
 
+
+// ---- GEMM fused with the all-gather of its column blocks ----------------------------------------------
+
+extern "C" int ck_b200_scaled_mm_nvfp4_all_gather(const void* a_dev, const void* sfa_dev, const void* b_dev,
+                                                  const void* sfb_dev, const float* tensor_scale_a_dev,
+                                                  const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
+                                                  const void* bias_dev_or_null, int bias_dtype, void* const* out_ptrs,
+                                                  int world, int rank, int out_dtype, int64_t M, int64_t N_local,
+                                                  int64_t K, void* stream) {
+    if (!out_ptrs || world < 1 || world > 8 || rank < 0 || rank >= world)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4_all_gather: need 1..8 ranks and 0 <= rank < world");
+    if (N_local < 0 || N_local % 8 != 0)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4_all_gather: N_local must be a multiple of 8");
+    GatherSpec spec;
+    spec.ld = (int64_t)world * N_local;
+    spec.n_peers = 0;
+    const int64_t block_bytes = (int64_t)rank * N_local * 2;   // 16-bit outputs only
+    for (int r = 0; r < world; ++r) {
+        if (!out_ptrs[r] || ((uintptr_t)out_ptrs[r] & 15))
+            return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4_all_gather: output %d is null or not 16-byte aligned", r);
+        // start with the rank after this one so that the ranks do not all write to the same peer at once
+        const int peer = (rank + 1 + r) % world;
+        if (peer != rank) spec.peers[spec.n_peers++] = (uint8_t*)out_ptrs[peer] + block_bytes;
+    }
+    void* own = (uint8_t*)out_ptrs[rank] + block_bytes;
+    return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
+                          bias_dev_or_null, bias_dtype, own, out_dtype, M, N_local, K, nullptr, 0, stream, &spec);
+}
+
+// ---- barrier between the ranks of one node ------------------------------------------------------------
+
+extern "C" int ck_b200_peer_barrier(void* const* flag_ptrs, int world, int rank, void* epoch_dev, void* stream) {
+    if (int rc = check_device(nullptr)) return rc;
+    if (!flag_ptrs || !epoch_dev || world < 1 || world > 8 || rank < 0 || rank >= world)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "peer_barrier: need 1..8 ranks, 0 <= rank < world and non-null pointers");
+    BarrierArgs b;
+    for (int r = 0; r < 8; ++r) b.flags[r] = r < world ? (uint32_t*)flag_ptrs[r] : nullptr;
+    for (int r = 0; r < world; ++r)
+        if (!b.flags[r] || ((uintptr_t)b.flags[r] & 3))
+            return fail(CK_B200_ERR_INVALID_ARGUMENT, "peer_barrier: flag array %d is null or misaligned", r);
+    b.epoch = (uint32_t*)epoch_dev;
+    b.world = world;
+    b.rank = rank;
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(b);
+    g_launches.fetch_add(1);
+    CKB_CUDA_OK(cudaGetLastError());
+    return CK_B200_OK;
+}
 
 // ---- entry point with built-in scratch --------------------------------------------------------------
 

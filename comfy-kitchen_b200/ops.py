@@ -183,6 +183,78 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
     return out
 
 
+def scaled_mm_nvfp4_all_gather(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tensor,
+                               tensor_scale_b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
+                               out_ptrs: list[int], rank: int, out_dtype: torch.dtype = torch.bfloat16,
+                               bias: torch.Tensor | None = None) -> None:
+    """scaled_mm_nvfp4 of this rank's weight shard ``b`` [N_local, K/2], written into columns
+    [rank*N_local, (rank+1)*N_local) of every rank's [M, world*N_local] matrix (``out_ptrs``: device addresses by rank,
+    peers' matrices as mapped by ``peer_open``).  Returns nothing: the matrices are complete after the next
+    ``peer_barrier`` on every rank."""
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    _require_cuda(a, "a")
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("scaled_mm_nvfp4_all_gather writes float16 or bfloat16")
+    m, k_half = a.shape
+    n_local = b.shape[0]
+    assert b.shape[1] == k_half and a.is_contiguous() and b.is_contiguous()
+    sk = roundup(2 * k_half // 16, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n_local, 128), sk), "Invalid B scale shape"
+    bias_code = 2
+    if bias is not None:
+        bias = _plain(bias)
+        assert bias.numel() == n_local and bias.is_contiguous() and bias.dtype in (torch.float16, torch.bfloat16)
+        bias_code = DTYPE_TO_CODE[bias.dtype]
+    world = len(out_ptrs)
+    arr = (ctypes.c_void_p * world)(*out_ptrs)
+    with torch.cuda.device(a.device):
+        tsa = _scale_on(a.device, tensor_scale_a)
+        tsb = _scale_on(a.device, tensor_scale_b)
+        rc = _lib.load().ck_b200_scaled_mm_nvfp4_all_gather(_ptr(a), _ptr(block_scale_a), _ptr(b), _ptr(block_scale_b),
+                                                            _ptr(tsa), _ptr(tsb), None, _ptr(bias), bias_code, arr, world,
+                                                            rank, DTYPE_TO_CODE[out_dtype], m, n_local, 2 * k_half,
+                                                            _stream(a.device))
+    _lib.check(rc, "scaled_mm_nvfp4_all_gather")
+
+
+def peer_barrier(flag_ptrs: list[int], rank: int, epoch: torch.Tensor) -> None:
+    """Enqueue a barrier between the ranks of the node on the current stream (``flag_ptrs``: every rank's flag array
+    as mapped here; ``epoch``: this rank's zero-initialised int32 counter)."""
+    world = len(flag_ptrs)
+    arr = (ctypes.c_void_p * world)(*flag_ptrs)
+    with torch.cuda.device(epoch.device):
+        rc = _lib.load().ck_b200_peer_barrier(arr, world, rank, _ptr(epoch), _stream(epoch.device))
+    _lib.check(rc, "peer_barrier")
+
+
+def peer_alloc(nbytes: int, device: torch.device) -> tuple[int, bytes]:
+    """Zeroed device memory other processes of the node can map: (address, 64-byte handle)."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().ck_b200_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
+    return int(ptr.value), handle.raw
+
+
+def peer_open(handle: bytes, device: torch.device) -> int:
+    ptr = ctypes.c_void_p()
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().ck_b200_peer_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(ptr)), "peer_open")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int, device: torch.device) -> None:
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().ck_b200_peer_close(ptr), "peer_close")
+
+
+def peer_free(ptr: int, device: torch.device) -> None:
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().ck_b200_peer_free(ptr), "peer_free")
+
+
 def dynamic_scale_nvfp4(x: torch.Tensor) -> torch.Tensor:
     """amax(|x|)/(448*6) evaluated in x's dtype and returned as a float32 scalar tensor on x's device: the
     per-tensor scale ``TensorCoreNVFP4Layout.quantize`` computes when none is given

@@ -4,9 +4,11 @@ The reference is single-GPU; this is the multi-GPU form of its NVFP4 linear
 (``samples/nvfp4_linear.py:39-80``: quantize the activation, ``F.linear`` on two NVFP4 tensors).  Each
 rank keeps rows ``[n0, n1)`` of the weight resident as packed e2m1 bytes with its own tiled scale tensor;
 the per-tensor weight scale is computed once from the whole weight so that every rank's columns equal the
-columns of the unsharded result.  The activation is replicated; every rank quantizes it, multiplies by its
-shard and the bf16 column blocks are exchanged with one all-gather (NCCL over NVLink on GPUs, gloo in
-the CPU tests of the host logic).
+columns of the unsharded result.  The activation is replicated; every rank quantizes it and multiplies by its
+shard.  The bf16 column blocks reach the other ranks in one of two ways: ``fused`` - the GEMM's epilogue stores
+each finished tile into every rank's output matrix over NVLink (``PeerGroup`` maps the matrices between the
+processes), so there is no collective after the GEMM - or ``gather`` / ``gather_async``, one all-gather through
+``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests of the host logic).
 """
 from __future__ import annotations
 
@@ -23,6 +25,81 @@ def shard_rows(n: int, world: int, rank: int, unit: int = 8) -> tuple[int, int]:
         raise ValueError(f"N = {n} must be a multiple of {unit}")
     u = n // unit
     return (rank * u // world) * unit, ((rank + 1) * u // world) * unit
+
+
+class _DeviceBytes:
+    """Lets torch view raw device memory (the CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerMemory:
+    """``nbytes`` of zeroed device memory on every rank, each rank's block mapped into all the others.
+    ``ptrs[r]`` is rank r's block as addressable from this process."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None, ops=None):
+        if ops is None:
+            from . import ops as _ops
+            ops = _ops
+        self.ops, self.device, self.nbytes = ops, torch.device(device), int(nbytes)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.own, handle = ops.peer_alloc(self.nbytes, self.device)
+        handles = [handle]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+        self.ptrs = [self.own if r == self.rank else ops.peer_open(handles[r], self.device) for r in range(self.world)]
+        self._closed = False
+
+    def tensor(self, shape, dtype: torch.dtype, offset: int = 0) -> torch.Tensor:
+        """A tensor over this rank's own block (no copy)."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        assert offset + nbytes <= self.nbytes
+        raw = torch.as_tensor(_DeviceBytes(self.own + offset, nbytes), device=self.device)
+        return raw.view(dtype).view(*shape)
+
+    def close(self) -> None:
+        """Unmap the peers' blocks and free this rank's; collective in spirit: no rank may still be writing."""
+        if self._closed:
+            return
+        self._closed = True
+        torch.cuda.synchronize(self.device)
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                self.ops.peer_close(p, self.device)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier()
+        self.ops.peer_free(self.own, self.device)
+
+
+class PeerGroup:
+    """The ranks of one node as seen by the fused kernels: mapped memory plus a stream-ordered barrier."""
+
+    def __init__(self, device: torch.device, group=None, ops=None):
+        self.device, self.group = torch.device(device), group
+        self.flags = PeerMemory(256, self.device, group, ops)
+        self.ops, self.world, self.rank = self.flags.ops, self.flags.world, self.flags.rank
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.blocks: list[PeerMemory] = [self.flags]
+
+    def alloc(self, nbytes: int) -> PeerMemory:
+        m = PeerMemory(nbytes, self.device, self.group, self.ops)
+        self.blocks.append(m)
+        return m
+
+    def barrier(self) -> None:
+        """Enqueue a barrier of all ranks on the current stream."""
+        self.ops.peer_barrier(self.flags.ptrs, self.rank, self.epoch)
+
+    def close(self) -> None:
+        for m in reversed(self.blocks):
+            m.close()
+        self.blocks = []
 
 
 class ShardedNVFP4Linear:
@@ -65,6 +142,32 @@ class ShardedNVFP4Linear:
         y = self.ops.scaled_mm_nvfp4(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
                                      bias=self.bias, out_dtype=x.dtype if x.dtype != torch.float32 else torch.bfloat16)
         return y[: x.shape[0], : self.local_rows]
+
+    def bind(self, peers: PeerGroup, m: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """Set up the fused path for activations of ``m`` rows: allocates this layer's [m, N] output matrix on every
+        rank (mapped everywhere) and returns this rank's, which ``fused`` fills.  Needs equal shards."""
+        sizes = {b - a for a, b in (shard_rows(self.out_features, self.world, r) for r in range(self.world))}
+        if len(sizes) != 1:
+            raise ValueError("the fused all-gather needs equal shards")
+        self.peers = peers
+        self._out_mem = peers.alloc(m * self.out_features * 2)
+        self._out_rows, self._out_dtype = m, dtype
+        self.out_full = self._out_mem.tensor((m, self.out_features), dtype)
+        return self.out_full
+
+    def fused(self, x: torch.Tensor) -> torch.Tensor:
+        """Quantize, multiply by this rank's shard and store the column block into every rank's output matrix from
+        the GEMM's epilogue.  Returns this rank's matrix, complete after the next ``peers.barrier()`` on all ranks;
+        a barrier must also separate a consumer of the matrix from the next call that overwrites it."""
+        assert x.shape[0] == self._out_rows, "bind() fixed the number of rows"
+        ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
+        pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
+        qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
+        if qx.shape[0] != x.shape[0]:
+            raise ValueError("the fused all-gather needs a row count that is a multiple of 16")
+        self.ops.scaled_mm_nvfp4_all_gather(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
+                                            self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias)
+        return self.out_full
 
     def gather_async(self, y_local: torch.Tensor):
         """Start the all-gather of equal column blocks and return ``(work, buffer)``: the collective runs on the

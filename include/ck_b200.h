@@ -5,7 +5,7 @@
  * This is the boundary a native binding of comfy-kitchen would call in place of the reference's
  * extern "C" launchers.  Every pointer named *_dev is device memory on the current CUDA device;
  * `stream` is a cudaStream_t passed as void*.  Calls only enqueue work: they never synchronise,
- * never allocate device memory and may be captured in a CUDA graph.  Every function returns 0 on
+ * never allocate device memory and may be captured in a CUDA graph (the ck_b200_peer_* set-up calls excepted).  Every function returns 0 on
  * success and a non-zero CK_B200_ERR_* code otherwise; nothing throws across this boundary and the
  * message for the calling thread's last failure is available from ck_b200_last_error().
  *
@@ -103,6 +103,49 @@ int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const void* sfa_de
                                            const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
                                            const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype,
                                            int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
+ * scaled_mm_nvfp4 of a column-parallel (N-sharded) linear fused with the all-gather of its output: the calling rank
+ * computes columns [rank*N_local, (rank+1)*N_local) of the [M, world*N_local] result and the kernel's epilogue
+ * stores every finished tile into that column block of EVERY rank's matrix - its own through TMA, the others'
+ * through stores to peer memory over NVLink - so no separate collective runs afterwards.  No counterpart in the
+ * reference, which is single-GPU (the multi-GPU form of comfy_kitchen/tensor/nvfp4.py:212-260).
+ *
+ *   out_ptrs   host array of `world` pointers: out_ptrs[r] is rank r's [M, world*N_local] 16-bit matrix as
+ *              addressable from this device (own memory for r == rank; ck_b200_peer_open mappings otherwise)
+ *   b_dev, sfb_dev, bias_dev_or_null   this rank's shard: [N_local, K/2], its tiled scales, [N_local]
+ *   out_dtype  1 or 2;  M > 128 and N_local > 128 (the CTA-pair kernel), N_local % 8 == 0;  1 <= world <= 8
+ * The stores to the peers are complete when the kernel has finished; a rank may read its matrix after a
+ * ck_b200_peer_barrier that follows the call on every rank (and must not overwrite a peer's matrix before that
+ * peer is done with it: a barrier before the call).
+ */
+int ck_b200_scaled_mm_nvfp4_all_gather(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                                       const float* tensor_scale_a_dev, const float* tensor_scale_b_dev,
+                                       const float* alpha_dev_or_null, const void* bias_dev_or_null, int bias_dtype,
+                                       void* const* out_ptrs, int world, int rank, int out_dtype, int64_t M,
+                                       int64_t N_local, int64_t K, void* stream);
+
+/*
+ * Barrier between the ranks of one node, enqueued on `stream` (one small kernel per rank; no host involvement, so it
+ * can be captured in a CUDA graph).  flag_ptrs[r] is rank r's array of `world` zero-initialised uint32 counters in
+ * peer-addressable memory, epoch_dev one zero-initialised uint32 in this rank's memory; every rank must enqueue the
+ * same sequence of barriers.  One rank per GPU: the kernels of different ranks wait for one another.  The wait is
+ * bounded (2 s): on expiry the kernel records code 6 in the status word (ck_b200_read_device_status) and returns.
+ * No counterpart in the reference.
+ */
+int ck_b200_peer_barrier(void* const* flag_ptrs, int world, int rank, void* epoch_dev, void* stream);
+
+/*
+ * Device memory the other ranks of the node can map (CUDA IPC), for the two calls above.  Set-up calls: they
+ * allocate, synchronise and are not for the hot path.  peer_alloc returns zeroed memory on the current device and
+ * writes its CK_B200_PEER_HANDLE_BYTES-byte handle, which the caller ships to the other processes (any transport);
+ * peer_open maps such a handle from another process; peer_close / peer_free undo them.  No counterpart in the reference.
+ */
+#define CK_B200_PEER_HANDLE_BYTES 64
+int ck_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out);
+int ck_b200_peer_open(const void* handle, void** ptr_out);
+int ck_b200_peer_close(void* ptr);
+int ck_b200_peer_free(void* ptr);
 
 /*
  * amax(|x|) / (448*6) computed in the input dtype and widened to float32, the per-tensor scale
