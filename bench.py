@@ -220,9 +220,13 @@ def run_ours(args, wl):
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    # N > 1 launches eagerly: a captured step (all-gathers included) ran 5 % faster on 2 GPUs but the process then
-    # hung while tearing the process group down, so collectives stay out of graphs
-    use_graph = not distributed and not args.no_graph
+    # N > 1, default: the GEMM's epilogue stores its tiles into every rank's output matrix (peer memory over
+    # NVLink) and the ranks meet at a stream-ordered barrier kernel before and after the step, so a step holds no
+    # library collective and is captured in a CUDA graph like the single-GPU step.  --collective nccl keeps the
+    # NCCL all-gather instead; it launches eagerly: a captured step with all-gathers in it ran 5 % faster on 2 GPUs
+    # but the process then hung while tearing the process group down, so library collectives stay out of graphs
+    fused = distributed and args.collective == "fused"
+    use_graph = (not distributed or fused) and not args.no_graph
 
     M = wl["M"]
     pad_m = M % 16 != 0
@@ -236,11 +240,24 @@ def run_ours(args, wl):
     graphs = []
 
     equal_shards = all(n % (8 * world) == 0 for _, _, n in wl["linears"])
+    peers = None
+    if fused and not (equal_shards and M % 16 == 0 and all(n // world > 128 for _, _, n in wl["linears"])):
+        fused = False            # the fused kernel wants equal shards wider than 128 columns and M % 16 == 0
+        use_graph = False
+    if fused:
+        peers = ckb.PeerGroup(dev)
+        for lin in layers:
+            lin.bind(peers, M)
 
     def step():
         # the linears of a step are independent work items: the all-gather of one overlaps the quantizer and GEMM
         # of the next (the collective runs on the process group's stream); all of them are awaited before the
         # step ends
+        if fused:
+            peers.barrier()                       # every rank is done with the previous step's matrices
+            outs = [lin.fused(x) for x, lin in zip(xs, layers)]
+            peers.barrier()                       # every rank's column blocks have arrived
+            return outs
         outs, pending = [], []
         for x, lin in zip(xs, layers):
             y = lin.local(x)
@@ -414,9 +431,15 @@ def run_ours(args, wl):
     def e2e_step():
         for xh, yh, lin in zip(x_host, y_host, layers):
             xd = xh.to(dev, non_blocking=True)
-            y = lin.local(xd)
-            if distributed:
-                y = lin.gather(y, row_major=False)[rank]
+            if fused:
+                peers.barrier()
+                y = lin.fused(xd)
+                peers.barrier()
+                y = y[:, lin.n0:lin.n1]
+            else:
+                y = lin.local(xd)
+                if distributed:
+                    y = lin.gather(y, row_major=False)[rank]
             yh.copy_(y, non_blocking=True)
 
     for _ in range(2):
@@ -451,7 +474,9 @@ def run_ours(args, wl):
             "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": wl["name"], "M": M, "linears": wl["linears"],
-                       "parallelism": f"weights N-sharded over {world} GPU(s)" + (", NCCL all-gather of bf16 outputs (overlapping the next linear)" if distributed else ""),
+                       "parallelism": f"weights N-sharded over {world} GPU(s)" + ((", all-gather of bf16 outputs fused into the GEMM epilogue (stores to peer memory over NVLink), "
+                                         "barrier kernel before and after the step") if fused else
+                                        ", NCCL all-gather of bf16 outputs (overlapping the next linear)" if distributed else ""),
                        "launch": "one CUDA graph per step" if use_graph else "eager launches",
                        "l2": "no flush: one step touches ~0.6 GB (activations, packed operands, outputs), 5x the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
@@ -459,7 +484,16 @@ def run_ours(args, wl):
             "quantize_gbs": quant_gbs, "gemm_only_tflops": gemm_tflops,
             "quantize_sweep": sweep,
         }
+        if fused:
+            # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate
+            out_bytes = sum(M * lin.local_rows * 2 for lin in layers) * (world - 1)
+            line["nvlink"] = {"bytes_out_per_rank_per_step": out_bytes,
+                              "achieved_gbs": out_bytes / (ms / args.steps * 1e-3) / 1e9, "peak_gbs": 770.0,
+                              "peak_source": "measured peer copy per direction on this pool",
+                              "note": "whole step in the denominator, quantizer kernels (no traffic) included"}
         print(json.dumps(line), flush=True)
+    if peers is not None:
+        peers.close()
     if distributed:
         dist.destroy_process_group()
 
@@ -475,6 +509,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantizer bandwidth sweep")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic stream serialisation")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: all-gather fused into the GEMM epilogue over peer memory, or a NCCL all-gather after it")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]

@@ -600,7 +600,7 @@ struct PairCfg {
     static constexpr int kSfa = kChunks * SF_CHUNK_BYTES;
     static constexpr int kSfb = 2 * kChunks * SF_CHUNK_BYTES;       // both 128-row bands of the B tile
     static constexpr int kStageBytes = kA + kB + kSfa + kSfb;       // 38 KiB or 19 KiB
-    static constexpr int kStagingBytes = 4 * 2 * STAGING_BYTES_PER_WARP;   // two staging tiles per epilogue warp
+    static constexpr int kStagingBytes = 4 * 4 * STAGING_BYTES_PER_WARP;   // four staging tiles per epilogue warp
     static constexpr int kStages = (232448 - 1024 - 256 - kStagingBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
     static constexpr uint32_t kLayout = (KB == 128) ? LAYOUT_SWIZZLE_128B : LAYOUT_SWIZZLE_64B;
@@ -827,12 +827,12 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
         const int quad = warp & 3;
         int acc = 0;
-        uint32_t acc_phase = 0, buf = 0;
+        uint32_t acc_phase = 0;
         bool ok = true;
         long long wait_acc = 0;
         const long long t_begin = now();
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
-        uint8_t* my_staging = staging + quad * 2 * STAGING_BYTES_PER_WARP;   // two tiles per warp
+        uint8_t* my_staging = staging + quad * 4 * STAGING_BYTES_PER_WARP;   // four tiles per warp: step s uses tile s % 4
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         const uint32_t overlap0 = map_to_cta(smem_u32(overlap_bar), 0);
         constexpr int kSteps = 256 / EPI_COLS;
@@ -849,15 +849,18 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int row0 = (tm * 2 + (int)rank) * BM + quad * 32;
             const int64_t row = (int64_t)row0 + lane;
             const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kAccCol1_2;
-            const int first_step = (acc == 0) ? kSteps - kOverlapSteps : 0;
-            auto emit = [&](int s, const uint32_t (&v)[32]) {
+            // order of the eight 32-column steps: accumulator 0 starts with the two steps whose columns it shares
+            // with accumulator 1 (6, 7), then finishes that group of four (4, 5) before 0..3, so that every four
+            // consecutive steps cover 128 adjacent columns
+            auto step_at = [&](int i) { return (acc == 0) ? ((i < 4) ? 4 + (i ^ 2) : i - 4) : i; };
+            auto emit = [&](int i, int s, const uint32_t (&v)[32]) {
                 const int n0 = tn * 256 + s * EPI_COLS;
                 float y[32];
                 scale_row32(g, n0, v, alpha, y);
                 if (g.tma_store) {
-                    if (lane == 0) tma_store_wait_read<1>();   // the store issued two steps ago has read its tile
+                    if (lane == 0) tma_store_wait_read<3>();   // the store issued four steps ago has read this tile
                     __syncwarp();
-                    uint8_t* tile_smem = my_staging + buf * STAGING_BYTES_PER_WARP;
+                    uint8_t* tile_smem = my_staging + (s & 3) * STAGING_BYTES_PER_WARP;
                     uint8_t* rowp = tile_smem + lane * 64;
                     const int sw = (lane >> 1) & 3;
 #pragma unroll
@@ -875,22 +878,25 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         tma_store_2d(&tmap_out, n0, row0, smem_u32(tile_smem));
                         tma_store_commit();
                     }
-                    if (g.n_peers > 0) {
-                        // the same tile to the other ranks: rows as 64-byte segments, four lanes per row and eight
-                        // rows per store instruction, read back from the staged (swizzled) tile
-                        const int c = lane & 3;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int r = (lane >> 2) + 8 * j;
-                            const uint4 o = *reinterpret_cast<const uint4*>(tile_smem + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
-                            if (row0 + r < g.M && n0 + c * 8 < g.N) {
-                                const int64_t off = ((int64_t)(row0 + r) * g.ld_out + n0 + c * 8) * 2;
+                    if (g.n_peers > 0 && (i & 3) == 3) {
+                        // the same columns to the other ranks, four steps at a time: the warp's four staging tiles
+                        // now hold 128 adjacent columns of its 32 rows, which go out as 256-byte row segments,
+                        // sixteen lanes per row and two rows per store instruction
+                        const int c = lane & 15;
+                        const uint8_t* src_tile = my_staging + (c >> 2) * STAGING_BYTES_PER_WARP;
+                        const int col = tn * 256 + (s & ~3) * EPI_COLS + c * 8;
+#pragma unroll 4
+                        for (int j = 0; j < 16; ++j) {
+                            const int r = (lane >> 4) + 2 * j;
+                            const uint4 o =
+                                *reinterpret_cast<const uint4*>(src_tile + r * 64 + (((c & 3) ^ ((r >> 1) & 3)) << 4));
+                            if (row0 + r < g.M && col < g.N) {
+                                const int64_t off = ((int64_t)(row0 + r) * g.ld_out + col) * 2;
 #pragma unroll 1
                                 for (int p = 0; p < g.n_peers; ++p) st_global_v4(g.peer_out[p] + off, o);
                             }
                         }
                     }
-                    buf ^= 1;
                 } else if (row < g.M && n0 < g.N) {
                     store_row32(g, row, n0, y);
                 }
@@ -898,25 +904,25 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             {
                 // both steps of the columns shared by the two accumulators are fetched first and handed to the
                 // next tile's MMAs before any output work
-                static_assert(kOverlapSteps == 2, "two epilogue steps cover the shared columns");
+                static_assert(kOverlapSteps == 2 && kSteps == 8, "two of eight epilogue steps cover the shared columns");
                 uint32_t v0[32], v1[32];
-                const int s0 = first_step % kSteps, s1 = (first_step + 1) % kSteps;
+                const int s0 = step_at(0), s1 = step_at(1);
                 tc_ld32(t_acc + s0 * EPI_COLS, v0);
                 tc_ld32(t_acc + s1 * EPI_COLS, v1);
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(overlap0);
-                emit(s0, v0);
-                emit(s1, v1);
+                emit(0, s0, v0);
+                emit(1, s1, v1);
             }
 #pragma unroll 1
             for (int i = 2; i < kSteps; ++i) {
-                const int s = (first_step + i) % kSteps;
+                const int s = step_at(i);
                 uint32_t v[32];
                 tc_ld32(t_acc + s * EPI_COLS, v);
                 tc_wait_ld();
-                emit(s, v);
+                emit(i, s, v);
             }
             tc_fence_before();
             __syncwarp();
