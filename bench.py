@@ -364,7 +364,10 @@ def run_ours(args, wl):
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     roofline = {
         "kernel": "gemm_nvfp4_kernel", "bound": "tensor", "achieved": gemm_tflops, "peak": NOMINAL_NVFP4_TFLOPS,
-        "unit": "TFLOP/s", "frac": gemm_tflops / NOMINAL_NVFP4_TFLOPS, "traffic": None,
+        "unit": "TFLOP/s", "frac": gemm_tflops / NOMINAL_NVFP4_TFLOPS,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch (mean of the four Flux launches) from the ncu capture
+        # summarised in profiles/gemm_nvfp4_pair_kernel_flux.md; other workloads / shard sizes were not captured
+        "traffic": 56.45e6 if (args.workload == "flux" and world == 1) else None,
         "peak_source": "nominal dense NVFP4 (vendor figure); MEASURED_PEAKS.json has no FP4 entry",
         "frac_of_4x_measured_bf16": (gemm_tflops / (4.0 * peaks["bf16_tflops"])) if "bf16_tflops" in peaks else None,
         "algorithmic_flops_per_launch": gemm_fl / len(layers), "avg_launch_us": gemm_ms * 1e3 / len(layers),
