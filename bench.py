@@ -216,6 +216,8 @@ def run_ours(args, wl):
     dev = torch.device("cuda", local_rank)
     if args.no_dependent_launch:
         ckb.set_tuning(3, 0)
+    elif args.dependent_launch_mask is not None:
+        ckb.set_tuning(3, args.dependent_launch_mask)
     distributed = world > 1
     if distributed:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -512,6 +514,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the quantizer bandwidth sweep")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic stream serialisation")
+    ap.add_argument("--dependent-launch-mask", type=int, default=None,
+                    help="which kernels get the programmatic-serialisation attribute: 1 GEMMs, 2 quantizers, 3 both")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather fused into the GEMM epilogue over peer memory, or a NCCL all-gather after it")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")

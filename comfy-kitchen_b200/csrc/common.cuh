@@ -46,9 +46,11 @@ static inline int64_t ceil_div64(int64_t x, int64_t m) { return (x + m - 1) / m;
 // stream is still draining, and runs its prologue up to grid_dependency_wait() before that kernel has finished.
 // Every kernel launched through here calls allow_dependent_launch() first thing and grid_dependency_wait() before
 // its first access to global memory, so ordering and visibility are those of a plain in-stream launch.
+// `family` selects the bit of the CK_B200_TUNE_DEPENDENT_LAUNCH mask that enables the attribute for this kernel.
+constexpr int kLaunchFamilyGemm = 1, kLaunchFamilyQuantize = 2;
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args... args) {
+inline cudaError_t launch_dependent(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -58,7 +60,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_dependent_launch.load() ? 1 : 0;
+    cfg.numAttrs = (g_dependent_launch.load() & family) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

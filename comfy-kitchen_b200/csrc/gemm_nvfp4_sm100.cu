@@ -1145,7 +1145,7 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     g.partial = nullptr;
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
-    const cudaError_t err = launch_dependent(kernel, dim3(grid), dim3(NUM_THREADS), kSmemBytes2, stream, ma, mb, msa, msb, mo, g);
+    const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), kSmemBytes2, stream, ma, mb, msa, msb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
     return CK_B200_OK;
@@ -1200,12 +1200,12 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     }
     const int64_t items = (int64_t)g.m_tiles * g.n_tiles * g.splits;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
-    const cudaError_t err = launch_dependent(kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
+    const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
     if (g.splits > 1) {
         const int64_t quads = (int64_t)g.M * g.N / 4;
-        const cudaError_t err2 = launch_dependent(splitk_reduce_kernel, dim3((unsigned)ceil_div64(quads, 256)), dim3(256), 0,
+        const cudaError_t err2 = launch_dependent(kLaunchFamilyGemm, splitk_reduce_kernel, dim3((unsigned)ceil_div64(quads, 256)), dim3(256), 0,
                                                   stream, g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias,
                                                   g.bias_dtype, g.out, g.out_dtype);
         g_launches.fetch_add(1);

@@ -134,6 +134,111 @@ struct Input<CK_B200_DTYPE_F32> {
     }
 };
 
+// ---- packed pairs of fp32 (sm_100 f32x2 arithmetic: one instruction, two results) ---------------------------
+
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+    f32x2_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2_t pack2_bits(uint32_t lo, uint32_t hi) {
+    f32x2_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t mul2_rn(f32x2_t a, f32x2_t b) {
+    f32x2_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t fma2_rn(f32x2_t a, f32x2_t b, f32x2_t c) {
+    f32x2_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2_t fma2_rm(f32x2_t a, f32x2_t b, f32x2_t c) {   // rounds toward minus infinity
+    f32x2_t r;
+    asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// max(|a|, |b|) per 16-bit half; the sign bits of the result are meaningless (xor of the inputs' signs)
+__device__ __forceinline__ uint32_t maxabs_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// Widened pairs of the eight elements of a unit, and the amax of the block that this lane derives.  The two lanes
+// of a pair each hold eight elements of two units; lane "X" data is the unit whose block the lane derives, lane "Y"
+// data the other unit, whose block the partner lane derives.  block_amax returns max(own X half, partner's Y half).
+template <int DT>
+struct Pairs;
+
+template <>
+struct Pairs<CK_B200_DTYPE_BF16> {
+    using Raw = Input<CK_B200_DTYPE_BF16>::Raw;
+    static __device__ __forceinline__ void widen(const Raw& r, f32x2_t (&f)[4]) {
+        const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = pack2_bits(w[i] << 16, w[i] & 0xffff0000u);
+    }
+    static __device__ __forceinline__ float block_amax(const Raw& x, const Raw& y) {
+        const uint32_t mx = maxabs_bf16x2(maxabs_bf16x2(x.v.x, x.v.y), maxabs_bf16x2(x.v.z, x.v.w));
+        const uint32_t my = maxabs_bf16x2(maxabs_bf16x2(y.v.x, y.v.y), maxabs_bf16x2(y.v.z, y.v.w));
+        // low half: this lane's X elements, high half: its Y elements
+        const uint32_t mine = maxabs_bf16x2(__byte_perm(mx, my, 0x5410), __byte_perm(mx, my, 0x7632));
+        const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, 1);
+        const uint32_t both = maxabs_bf16x2(mine, __byte_perm(theirs, theirs, 0x1032));   // low: X half, partner's Y half
+        return __uint_as_float((both << 16) & 0x7fff0000u);
+    }
+};
+
+template <>
+struct Pairs<CK_B200_DTYPE_F16> {
+    using Raw = Input<CK_B200_DTYPE_F16>::Raw;
+    static __device__ __forceinline__ void widen(const Raw& r, f32x2_t (&f)[4]) {
+        const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[i] = pack2(p.x, p.y);
+        }
+    }
+    static __device__ __forceinline__ float half_amax(const Raw& r) {
+        const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+        __half2 m = __habs2(*reinterpret_cast<const __half2*>(&w[0]));
+#pragma unroll
+        for (int i = 1; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __half2*>(&w[i])));
+        const float2 p = __half22float2(m);
+        return fmaxf(p.x, p.y);
+    }
+    static __device__ __forceinline__ float block_amax(const Raw& x, const Raw& y) {
+        return fmaxf(half_amax(x), __shfl_xor_sync(0xffffffffu, half_amax(y), 1));
+    }
+};
+
+template <>
+struct Pairs<CK_B200_DTYPE_F32> {
+    using Raw = Input<CK_B200_DTYPE_F32>::Raw;
+    static __device__ __forceinline__ void widen(const Raw& r, f32x2_t (&f)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = pack2_bits((&r.v[0].x)[2 * i], (&r.v[0].x)[2 * i + 1]);
+    }
+    static __device__ __forceinline__ float half_amax(const Raw& r) {
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(__uint_as_float((&r.v[0].x)[i])));
+        return m;
+    }
+    static __device__ __forceinline__ float block_amax(const Raw& x, const Raw& y) {
+        return fmaxf(half_amax(x), __shfl_xor_sync(0xffffffffu, half_amax(y), 1));
+    }
+};
+
 // ---- exact arithmetic helpers ---------------------------------------------------------------------
 
 // Correctly rounded a / b from rb = RN(1/b): two rounds of residual correction (Markstein).  The first round
@@ -222,6 +327,26 @@ __device__ __forceinline__ uint32_t quantize8_markstein(const float (&f)[8], flo
     for (int i = 0; i < 8; ++i) {
         const float q0 = __fmul_rn(f[i], r);
         d[i] = __fmaf_rn(__fmaf_rd(-t, q0, f[i]), r, q0);
+    }
+    return pack8_e2m1_hi_first(d);
+}
+
+// RN(1/t) for normal t without the range checks of the library routine: one MUFU reciprocal (within 1 ulp) and one
+// Newton step in fused arithmetic.  Equal to __frcp_rn for every fp32 in [2^-69, 2^69] (checked exhaustively on a B200).
+__device__ __forceinline__ float rcp_rn_normal(float t) {
+    float r0;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(t));
+    return fmaf(r0, fmaf(-t, r0, 1.0f), r0);
+}
+
+// quantize8_markstein on four packed pairs: three packed instructions per two elements.
+__device__ __forceinline__ uint32_t quantize8_markstein_packed(const f32x2_t (&f)[4], float t, float r) {
+    const f32x2_t tt = pack2(-t, -t), rr = pack2(r, r);
+    float d[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const f32x2_t q0 = mul2_rn(f[i], rr);
+        unpack2(fma2_rn(fma2_rm(tt, q0, f[i]), rr, q0), d[2 * i], d[2 * i + 1]);
     }
     return pack8_e2m1_hi_first(d);
 }
@@ -390,6 +515,118 @@ __device__ __forceinline__ void walk_interior(const LaneCtx& c, int u_begin, int
     }
 }
 
+// The pair of units of quantize_pair with lane-relative roles and no rare-path work in the common case: `raw_x` is the
+// unit whose block this lane derives (unit A on even lanes, unit B on odd lanes), `raw_y` the other one, so nothing
+// is selected by lane parity - the caller's addresses differ instead.  Everything is computed as if the block were
+// ordinary (finite, per-tensor scale and amax inside the exact-reciprocal range, or an all-zero block); one vote
+// at the end sends the whole warp to IEEE arithmetic otherwise.  Returns this lane's scale byte in s8.
+template <int DT>
+__device__ __forceinline__ void quantize_pair_xy(const LaneCtx& c, const typename Input<DT>::Raw& raw_x,
+                                                 const typename Input<DT>::Raw& raw_y, uint32_t& word_x,
+                                                 uint32_t& word_y, uint32_t& s8) {
+    using In = Input<DT>;
+    const float amax = Pairs<DT>::block_amax(raw_x, raw_y);
+    const bool ordinary = c.ts_in_range && (amax == 0.0f || (amax >= 0x1p-60f && amax <= 0x1p60f));
+    float t;
+    block_scale(amax, c.ts, c.rcp_ts, true, s8, t);   // t is 0 or inside [2^-69, 2^69] for an ordinary block
+    const float r = rcp_rn_normal(t);
+    const float t_y = __shfl_xor_sync(0xffffffffu, t, 1);
+    const float r_y = __shfl_xor_sync(0xffffffffu, r, 1);
+    f32x2_t fx[4], fy[4];
+    Pairs<DT>::widen(raw_x, fx);
+    Pairs<DT>::widen(raw_y, fy);
+    word_x = quantize8_markstein_packed(fx, t, r);
+    word_y = quantize8_markstein_packed(fy, t_y, r_y);
+    // zero decode scale: every element encodes +0 (the arithmetic above produced infinities or NaNs there)
+    word_x = (t == 0.0f) ? 0u : word_x;
+    word_y = (t_y == 0.0f) ? 0u : word_y;
+    if (!__all_sync(0xffffffffu, ordinary)) {
+        float gx[8], gy[8], t2;
+        In::unpack(raw_x, gx);
+        In::unpack(raw_y, gy);
+        block_scale(amax, c.ts, 0.0f, false, s8, t2);
+        const float t2_y = __shfl_xor_sync(0xffffffffu, t2, 1);
+        word_x = quantize8_exact(gx, t2);
+        word_y = quantize8_exact(gy, t2_y);
+    }
+    if (!c.hi_first) {
+        word_x = swap_nibbles32(word_x);
+        word_y = swap_nibbles32(word_y);
+    }
+}
+
+// walk_interior for quantize_pair_xy: even lanes keep unit A of a pair in raw[k] and unit B in raw[k + 1], odd lanes
+// the other way round, by a per-lane offset on the load and store addresses.
+// ROWS_IN = false: some of the warp's rows lie in the zero padding below the input (they are still rows of the
+// output); their lanes skip the loads and quantize zeros.
+template <int DT, bool ROWS_IN>
+__device__ __forceinline__ void walk_interior_xy(const LaneCtx& c, int u_begin, int u_end) {
+    using In = Input<DT>;
+    using Raw = typename In::Raw;
+    constexpr int kUnitBytes = 64 * In::kBytes;
+    const int sub = c.sub;
+    const int x_unit = c.odd ? 1 : 0, y_unit = 1 - x_unit;
+    const char* xp = c.x_row + (u_begin * 64 + sub * 8) * In::kBytes;
+    const char* xp_x = xp + x_unit * kUnitBytes;
+    const char* xp_y = xp + y_unit * kUnitBytes;
+    uint8_t* qp_x = c.q_row + (u_begin + x_unit) * 32 + sub * 4;
+    uint8_t* qp_y = c.q_row + (u_begin + y_unit) * 32 + sub * 4;
+    uint8_t* sp = c.sf_row + (u_begin + (sub & 1)) * 512;   // lane sub = 1 stores unit B's scales
+    const bool sf_lane = sub < 2;
+    int remaining = u_end - u_begin;   // even
+    auto load = [&](const char* p) -> Raw { return (ROWS_IN || c.row_in) ? In::load_vec(p) : In::zero(); };
+
+    Raw raw[kRing];
+#pragma unroll
+    for (int k = 0; k < kRing; k += 2) {
+        if (k < remaining) {
+            raw[k] = load(xp_x + k * kUnitBytes);
+            raw[k + 1] = load(xp_y + k * kUnitBytes);
+        } else {
+            raw[k] = In::zero();
+            raw[k + 1] = In::zero();
+        }
+    }
+
+    auto consume = [&](int k) {
+        uint32_t wx, wy, s8;
+        quantize_pair_xy<DT>(c, raw[k], raw[k + 1], wx, wy, s8);
+        *reinterpret_cast<uint32_t*>(qp_x + k * 32) = wx;
+        *reinterpret_cast<uint32_t*>(qp_y + k * 32) = wy;
+        const uint32_t sfw = gather_scale_word(s8, sub);
+        if (sf_lane) *reinterpret_cast<uint32_t*>(sp + k * 512) = sfw;
+    };
+    auto advance = [&] {
+        xp_x += kRing * kUnitBytes;
+        xp_y += kRing * kUnitBytes;
+        qp_x += kRing * 32;
+        qp_y += kRing * 32;
+        sp += kRing * 512;
+    };
+
+    for (; remaining >= 2 * kRing; remaining -= kRing) {
+#pragma unroll
+        for (int k = 0; k < kRing; k += 2) {
+            consume(k);
+            raw[k] = load(xp_x + (kRing + k) * kUnitBytes);
+            raw[k + 1] = load(xp_y + (kRing + k) * kUnitBytes);
+        }
+        advance();
+    }
+#pragma unroll 1
+    for (; remaining > 0; remaining -= kRing) {
+#pragma unroll
+        for (int k = 0; k < kRing; k += 2) {
+            if (k < remaining) consume(k);                    // uniform
+            if (kRing + k < remaining) {                      // uniform; pairs are whole
+                raw[k] = load(xp_x + (kRing + k) * kUnitBytes);
+                raw[k + 1] = load(xp_y + (kRing + k) * kUnitBytes);
+            }
+        }
+        advance();
+    }
+}
+
 // Edge segment: rows past the input, ragged columns, padding to 16x16 and to whole scale chunks.
 template <int DT, bool VEC, int VARIANT>
 __device__ __forceinline__ void walk_edge(const LaneCtx& c, int u_begin, int u_end) {
@@ -455,8 +692,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(
     allow_dependent_launch();
     const int lane = threadIdx.x;
     const int seg = blockIdx.x * blockDim.y + threadIdx.y;
-    const int group = (blockIdx.z * 65535 + blockIdx.y) * blockDim.z + threadIdx.z;
-    if (seg >= a.segments || group >= a.row_groups) return;   // whole warps
+    // row groups are handed out last band first: the bottom band is the one that may hold padding rows, whose
+    // warps take the slower edge walk and should not be the ones the kernel ends on
+    const int group = a.row_groups - 1 - (int)((blockIdx.z * 65535 + blockIdx.y) * blockDim.z + threadIdx.z);
+    if (seg >= a.segments || group < 0) return;   // whole warps
     const int u_begin = seg * a.seg_units;
     const int u_end = min(a.sf_cbg, u_begin + a.seg_units);
     const int d4 = lane >> 3;
@@ -479,8 +718,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(
     c.q_row = a.q + (int64_t)r * (a.pcol >> 1);
     c.sf_row = a.sf + (((int64_t)band * a.sf_cbg) * 32 + d3) * 16 + d4 * 4;
     // rows of the warp are r0 + {0,32,64,96}: all inside the input iff the last one is; segments hold whole pairs
-    const bool interior = VEC && (band * 128 + d3 + 96 < a.rows) && (u_end * 64 <= a.cols) && ((u_end - u_begin) % 2 == 0);
-    if (interior) walk_interior<DT, VARIANT>(c, u_begin, u_end);
+    const bool whole_pairs = VEC && (u_end * 64 <= a.cols) && ((u_end - u_begin) % 2 == 0);
+    const bool interior = whole_pairs && (band * 128 + d3 + 96 < a.rows);
+    if (interior && VARIANT == 2) walk_interior_xy<DT, true>(c, u_begin, u_end);
+    else if (VARIANT == 2 && whole_pairs && (band * 128 + d3 + 96 < a.prow)) walk_interior_xy<DT, false>(c, u_begin, u_end);
+    else if (interior) walk_interior<DT, VARIANT>(c, u_begin, u_end);
     else walk_edge<DT, VEC, VARIANT>(c, u_begin, u_end);
 }
 
@@ -522,13 +764,13 @@ int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t st
               (unsigned)ceil_div64(gy_total, 65535));
     cudaError_t err;
     if (vec) {
-        if (variant == 0) err = launch_dependent(quantize_nvfp4_kernel<DT, true, 0>, grid, block, 0, stream, a);
-        else if (variant == 2) err = launch_dependent(quantize_nvfp4_kernel<DT, true, 2>, grid, block, 0, stream, a);
-        else err = launch_dependent(quantize_nvfp4_kernel<DT, true, 1>, grid, block, 0, stream, a);
+        if (variant == 0) err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, true, 0>, grid, block, 0, stream, a);
+        else if (variant == 2) err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, true, 2>, grid, block, 0, stream, a);
+        else err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, true, 1>, grid, block, 0, stream, a);
     } else {
-        if (variant == 0) err = launch_dependent(quantize_nvfp4_kernel<DT, false, 0>, grid, block, 0, stream, a);
-        else if (variant == 2) err = launch_dependent(quantize_nvfp4_kernel<DT, false, 2>, grid, block, 0, stream, a);
-        else err = launch_dependent(quantize_nvfp4_kernel<DT, false, 1>, grid, block, 0, stream, a);
+        if (variant == 0) err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, false, 0>, grid, block, 0, stream, a);
+        else if (variant == 2) err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, false, 2>, grid, block, 0, stream, a);
+        else err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_kernel<DT, false, 1>, grid, block, 0, stream, a);
     }
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
@@ -586,7 +828,6 @@ __global__ void __launch_bounds__(256) dequantize_nvfp4_kernel(const uint8_t* __
                                                                int64_t rows, int64_t words_per_row, int sf_cbg,
                                                                int hi_first) {
     using Out = Output<DT>;
-    allow_dependent_launch();
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= rows * words_per_row) return;
     grid_dependency_wait();
@@ -708,13 +949,13 @@ extern "C" int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tens
     cudaError_t err;
     switch (out_dtype) {
         case CK_B200_DTYPE_F32:
-            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_F32>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F32>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
         case CK_B200_DTYPE_F16:
-            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_F16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
         default:
-            err = launch_dependent(dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
             break;
     }
     g_launches.fetch_add(1);
