@@ -405,6 +405,36 @@ def run_ours(args, wl):
             graphs.clear()
         torch.cuda.empty_cache()
 
+    # ---- small-M sweep (BASELINE configuration 5: T5-XXL-style feed-forward, d = 4096, ff = 10240), single-GPU runs:
+    # latency of one linear (quantize + GEMM, split-K below 129 rows) per M ----
+    small_m = None
+    if not distributed and not args.no_sweep:
+        small_m = []
+        gsm = torch.Generator(device=dev).manual_seed(5)
+        for (sk, sn) in [(4096, 10240), (10240, 4096)]:
+            ww = torch.randn((sn, sk), generator=gsm, device=dev, dtype=torch.bfloat16) * 0.02
+            wts = ckb.dynamic_scale_nvfp4(ww)
+            wq, wsf = ckb.quantize_nvfp4(ww, wts)
+            for sm in (1, 16, 64, 512):
+                xx = torch.randn((sm, sk), generator=gsm, device=dev, dtype=torch.bfloat16)
+                tt = ckb.dynamic_scale_nvfp4(xx)
+                qq, ss = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
+                def lin_call(xx=xx, tt=tt, wq=wq, wts=wts, wsf=wsf):
+                    q1, s1 = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
+                    return ckb.scaled_mm_nvfp4(q1, wq, tt, wts, s1, wsf)
+                r_l, _ = graphed(lin_call)
+                r_g, _ = graphed(lambda: ckb.scaled_mm_nvfp4(qq, wq, tt, wts, ss, wsf))
+                reps = 50
+                t_l = timed(r_l, reps) / reps
+                t_g = timed(r_g, reps) / reps
+                small_m.append({"M": sm, "K": sk, "N": sn, "linear_us": t_l * 1e3, "gemm_us": t_g * 1e3,
+                                "gemm_tflops": 2.0 * sm * sn * sk / (t_g * 1e-3) / 1e12,
+                                "weight_gbs": sn * sk * 0.5625 / (t_g * 1e-3) / 1e9})
+                del r_l, r_g
+                graphs.clear()
+            del ww, wq, wsf
+        torch.cuda.empty_cache()
+
     # ---- cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend ----
     try:
         from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
@@ -487,7 +517,7 @@ def run_ours(args, wl):
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "gemm_only_tflops": gemm_tflops,
-            "quantize_sweep": sweep,
+            "quantize_sweep": sweep, "small_m_sweep": small_m,
         }
         if fused:
             # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate
