@@ -360,6 +360,18 @@ def run_ours(args, wl):
         quant_ms += tq
         gemm_fl += 2.0 * M * n_local * k
         quant_bytes += M * k * 2.5625
+    # quantizer alone, row-sharded (the "GB/s at 1/2/4/8 GPU" reading of the metric): every rank quantizes its own
+    # M/G rows of each activation, no exchange; aggregate = all ranks' bytes over the slowest rank's time
+    row_sharded = None
+    if distributed:
+        r0, r1 = (rank * (M // 16) // world) * 16, ((rank + 1) * (M // 16) // world) * 16 if rank + 1 < world else M
+        t_rows = 0.0
+        for i in range(len(layers)):
+            x_rows = xs[i][r0:r1]
+            rs, _ = graphed(lambda x_rows=x_rows, i=i: ckb.quantize_nvfp4(x_rows, ts_x[i], pad_16x=True))
+            t_rows += timed(rs, args.steps) / args.steps
+        row_sharded = {"aggregate_gbs": quant_bytes / (t_rows * 1e-3) / 1e9, "rows_per_rank": r1 - r0,
+                       "us_per_step": t_rows * 1e3, "note": "weak in bytes per rank / strong in total: M rows split over the ranks"}
     peaks = measured_peaks()
     gemm_tflops = gemm_fl / (gemm_ms * 1e-3) / 1e12
     quant_gbs = quant_bytes / (quant_ms * 1e-3) / 1e9
@@ -484,6 +496,14 @@ def run_ours(args, wl):
            "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
            "what": "pinned host bf16 activations -> device, quantize_nvfp4 + scaled_mm_nvfp4 through the operator "
                    "interface, bf16 outputs -> pinned host; per rank"}
+    if args.gemm_debug and rank == 0:
+        # one launch per linear of the kernel build with cycle counters: CTA pair 0 prints (device printf, on stdout
+        # before the JSON line) the cycles and nanoseconds its roles took and how long they waited
+        ckb.set_tuning(2, 1)
+        for i in range(len(layers)):
+            one_gemm(i)()
+            torch.cuda.synchronize()
+        ckb.set_tuning(2, 0)
     status = ckb.read_device_status()
     clocks = sampler.stop() if rank == 0 else {}
 
@@ -516,7 +536,7 @@ def run_ours(args, wl):
                        "l2": "no flush: one step touches ~0.6 GB (activations, packed operands, outputs), 5x the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "cublaslt_comparator": cublaslt, "device_status": status,
-            "quantize_gbs": quant_gbs, "gemm_only_tflops": gemm_tflops,
+            "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
             "quantize_sweep": sweep, "small_m_sweep": small_m,
         }
         if fused:
@@ -548,6 +568,8 @@ def main():
                     help="which kernels get the programmatic-serialisation attribute: 1 GEMMs, 2 quantizers, 3 both")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather fused into the GEMM epilogue over peer memory, or a NCCL all-gather after it")
+    ap.add_argument("--gemm-debug", action="store_true",
+                    help="also launch each linear's GEMM once with in-kernel cycle counters (prints extra lines)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]

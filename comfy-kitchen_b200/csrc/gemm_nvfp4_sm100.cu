@@ -830,7 +830,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         uint32_t acc_phase = 0;
         bool ok = true;
         long long wait_acc = 0;
+        auto now_ns = [] {
+            long long t = 0;
+            if (DBG) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            return t;
+        };
         const long long t_begin = now();
+        const long long t_begin_ns = now_ns();
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
         uint8_t* my_staging = staging + quad * 4 * STAGING_BYTES_PER_WARP;   // four tiles per warp: step s uses tile s % 4
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
@@ -932,8 +938,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         if (g.tma_store && lane == 0) tma_store_wait_all();
         if (DBG && pair == 0 && threadIdx.x == 64)
-            printf("[gemm pair cta%u] epilogue: total %lld cycles, waiting for accumulators %lld\n", rank, now() - t_begin,
-                   wait_acc);
+            printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank,
+                   now() - t_begin, now_ns() - t_begin_ns, wait_acc);
     }
 
     tc_fence_before();
