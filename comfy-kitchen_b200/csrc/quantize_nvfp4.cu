@@ -819,50 +819,108 @@ struct Output<CK_B200_DTYPE_F32> {
     }
 };
 
-// One thread decodes 4 packed bytes (half of a 16-element block).  Rounding follows the eager backend:
+// One thread decodes 4 packed bytes (half of a 16-element block) at a time, kDequantIter of them per pass so that their
+// loads are in flight together.  Block (32, 8): a warp owns one row, its lanes consecutive 4-byte words (16-byte
+// outputs), so loads and stores are fully coalesced and nothing is divided.  Rounding follows the eager backend:
 // total = out(out(ts) * out(block_scale)), y = out(lut * total)  (eager/quantization.py:213-219).
+constexpr int kDequantIter = 4;
 template <int DT>
 __global__ void __launch_bounds__(256) dequantize_nvfp4_kernel(const uint8_t* __restrict__ q,
                                                                const float* __restrict__ pts,
                                                                const uint8_t* __restrict__ sf, void* __restrict__ out,
-                                                               int64_t rows, int64_t words_per_row, int sf_cbg,
-                                                               int hi_first) {
+                                                               int rows, int words_per_row, int sf_cbg, int hi_first) {
     using Out = Output<DT>;
-    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= rows * words_per_row) return;
+    const int lane = threadIdx.x;
+    const int r = blockIdx.x * 8 + threadIdx.y;
+    if (r >= rows) return;   // whole warps
     grid_dependency_wait();
-    const int64_t r = gid / words_per_row;
-    const int64_t h = gid % words_per_row;
-    uint32_t w = ldg_stream4(q + gid * 4);
-    if (!hi_first) w = swap_nibbles32(w);
     const float ts_o = Out::round(__ldg(pts));
-    const float bs_o = Out::round(e4m3_to_f32(__ldg(sf + sf_offset(r, (int)(h >> 1), sf_cbg))));
-    const float total = Out::round(__fmul_rn(ts_o, bs_o));
-    float y[8];
+    // scale (r, c) lives at sf_row + (c / 4) * 512 + c % 4 in the 128x4 tiled layout
+    const uint8_t* sf_row = sf + ((int64_t)(r >> 7) * sf_cbg * 32 + (r & 31)) * 16 + ((r & 127) >> 5) * 4;
+    const uint8_t* q_row = q + (int64_t)r * words_per_row * 4;
+    const int64_t out_row = (int64_t)r * words_per_row * 8;
+    for (int base = blockIdx.y * (32 * kDequantIter); base < words_per_row; base += gridDim.y * (32 * kDequantIter)) {
+        uint32_t w[kDequantIter];
+        uint32_t sb[kDequantIter];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t h2;
-        uint16_t byte = (uint16_t)((w >> (8 * i)) & 0xffu);
-        // low nibble -> low half, high nibble -> high half
-        asm("{\n.reg .b8 b, z;\nmov.b16 {b, z}, %1;\ncvt.rn.f16x2.e2m1x2 %0, b;\n}" : "=r"(h2) : "h"(byte));
-        float2 p = __half22float2(*reinterpret_cast<__half2*>(&h2));
-        y[2 * i] = Out::round(__fmul_rn(p.y, total));       // element 2i sits in the high nibble
-        y[2 * i + 1] = Out::round(__fmul_rn(p.x, total));
+        for (int i = 0; i < kDequantIter; ++i) {
+            const int wi = base + lane + 32 * i;
+            w[i] = 0;
+            sb[i] = 0;
+            if (wi < words_per_row) {
+                w[i] = ldg_stream4(q_row + wi * 4);
+                const int c = wi >> 1;
+                sb[i] = __ldg(sf_row + (c >> 2) * 512 + (c & 3));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kDequantIter; ++i) {
+            const int wi = base + lane + 32 * i;
+            if (wi >= words_per_row) break;
+            uint32_t word = w[i];
+            if (!hi_first) word = swap_nibbles32(word);
+            const float bs_o = Out::round(e4m3_to_f32((uint8_t)sb[i]));
+            const float total = Out::round(__fmul_rn(ts_o, bs_o));
+            float y[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t h2;
+                uint16_t byte = (uint16_t)((word >> (8 * k)) & 0xffu);
+                // low nibble -> low half, high nibble -> high half
+                asm("{\n.reg .b8 b, z;\nmov.b16 {b, z}, %1;\ncvt.rn.f16x2.e2m1x2 %0, b;\n}" : "=r"(h2) : "h"(byte));
+                float2 p = __half22float2(*reinterpret_cast<__half2*>(&h2));
+                y[2 * k] = Out::round(__fmul_rn(p.y, total));       // element 2k sits in the high nibble
+                y[2 * k + 1] = Out::round(__fmul_rn(p.x, total));
+            }
+            Out::store8(out, out_row + (int64_t)wi * 8, y);
+        }
     }
-    Out::store8(out, r * (words_per_row * 8) + h * 8, y);
 }
 
 // ---- dynamic per-tensor scale ---------------------------------------------------------------------
 
+// amax(|x|) over the whole tensor into *acc (bits of a non-negative float, combined with atomicMax).  16-byte loads,
+// four in flight per thread; the maximum is taken in the input dtype, which widening to fp32 preserves exactly.
 template <int DT>
 __global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ x, int64_t n, uint32_t* __restrict__ acc) {
+    constexpr int kPerVec = (DT == CK_B200_DTYPE_F32) ? 4 : 8;
     float m = 0.0f;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    const int64_t vecs = aligned ? n / kPerVec : 0;
+    auto fold = [&](const uint4& v) {
+        if (DT == CK_B200_DTYPE_BF16) {
+            const uint32_t p = maxabs_bf16x2(maxabs_bf16x2(v.x, v.y), maxabs_bf16x2(v.z, v.w));
+            m = fmaxf(m, fmaxf(__uint_as_float((p << 16) & 0x7fff0000u), __uint_as_float(p & 0x7fff0000u)));
+        } else if (DT == CK_B200_DTYPE_F16) {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            __half2 h = __habs2(*reinterpret_cast<const __half2*>(&w[0]));
+#pragma unroll
+            for (int i = 1; i < 4; ++i) h = __hmax2(h, __habs2(*reinterpret_cast<const __half2*>(&w[i])));
+            const float2 p = __half22float2(h);
+            m = fmaxf(m, fmaxf(p.x, p.y));
+        } else {
+            m = fmaxf(fmaxf(m, fabsf(__uint_as_float(v.x))), fabsf(__uint_as_float(v.y)));
+            m = fmaxf(fmaxf(m, fabsf(__uint_as_float(v.z))), fabsf(__uint_as_float(v.w)));
+        }
+    };
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    int64_t i = tid;
+    for (; i + 3 * stride < vecs; i += 4 * stride) {
+        const uint4 a = ldg_stream16(xv + i), b = ldg_stream16(xv + i + stride), c = ldg_stream16(xv + i + 2 * stride),
+                    d = ldg_stream16(xv + i + 3 * stride);
+        fold(a);
+        fold(b);
+        fold(c);
+        fold(d);
+    }
+    for (; i < vecs; i += stride) fold(ldg_stream16(xv + i));
+    for (int64_t j = vecs * kPerVec + tid; j < n; j += stride) {   // tail, or everything when the base is unaligned
         float v;
-        if (DT == CK_B200_DTYPE_F32) v = ((const float*)x)[i];
-        else if (DT == CK_B200_DTYPE_F16) v = __half2float(((const __half*)x)[i]);
-        else v = __bfloat162float(((const __nv_bfloat16*)x)[i]);
+        if (DT == CK_B200_DTYPE_F32) v = ((const float*)x)[j];
+        else if (DT == CK_B200_DTYPE_F16) v = __half2float(((const __half*)x)[j]);
+        else v = __bfloat162float(((const __nv_bfloat16*)x)[j]);
         m = fmaxf(m, fabsf(v));
     }
 #pragma unroll
@@ -938,9 +996,11 @@ extern "C" int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tens
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "dequantize_nvfp4: q must be 4-byte and out 16-byte aligned");
     if (rows == 0 || packed_cols == 0) return CK_B200_OK;
     const int64_t words_per_row = packed_cols / 4;
-    const int64_t total = rows * words_per_row;
-    const int64_t blocks = ceil_div64(total, 256);
-    if (blocks > 0x7fffffffll) return fail(CK_B200_ERR_INVALID_ARGUMENT, "dequantize_nvfp4: tensor too large");
+    if (rows > 0x3fffff00ll || words_per_row > 0x3fffff00ll)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "dequantize_nvfp4: rows and packed columns must be below 2^30");
+    const int64_t col_chunks = ceil_div64(words_per_row, 32 * kDequantIter);
+    const dim3 grid((unsigned)ceil_div64(rows, 8), (unsigned)(col_chunks < 65535 ? col_chunks : 65535));
+    const dim3 block(32, 8);
     const int sf_cbg = (int)(round_up64(packed_cols / 8, 4) / 4);
     cudaStream_t s = (cudaStream_t)stream;
     const uint8_t* q = (const uint8_t*)q_dev;
@@ -949,13 +1009,13 @@ extern "C" int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tens
     cudaError_t err;
     switch (out_dtype) {
         case CK_B200_DTYPE_F32:
-            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F32>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F32>, grid, block, 0, s, q, per_tensor_scale_dev, sf, out_dev, (int)rows, (int)words_per_row, sf_cbg, hf);
             break;
         case CK_B200_DTYPE_F16:
-            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_F16>, grid, block, 0, s, q, per_tensor_scale_dev, sf, out_dev, (int)rows, (int)words_per_row, sf_cbg, hf);
             break;
         default:
-            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16>, dim3((unsigned)blocks), dim3(256), 0, s, q, per_tensor_scale_dev, sf, out_dev, rows, words_per_row, sf_cbg, hf);
+            err = launch_dependent(kLaunchFamilyQuantize, dequantize_nvfp4_kernel<CK_B200_DTYPE_BF16>, grid, block, 0, s, q, per_tensor_scale_dev, sf, out_dev, (int)rows, (int)words_per_row, sf_cbg, hf);
             break;
     }
     g_launches.fetch_add(1);
