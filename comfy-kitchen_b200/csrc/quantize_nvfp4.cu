@@ -273,6 +273,19 @@ __device__ __forceinline__ void block_scale(float amax, float ts, float rcp_ts, 
     t = __fmul_rn(ts, e4m3_to_f32((uint8_t)s8));
 }
 
+// block_scale for an ordinary block (finite, non-negative quotient) with the conversions written as the two
+// instructions they are: no NaN handling, no branches.  Same results as block_scale(..., fast = true, ...) there.
+__device__ __forceinline__ void block_scale_ordinary(float amax, float ts, float rcp_ts, uint32_t& s8, float& t) {
+    const float bs = div_by_reciprocal(amax, 6.0f, 0x1.555556p-3f);   // RN(1/6)
+    const float sbs = fminf(div_by_reciprocal(bs, ts, rcp_ts), 448.0f);
+    uint16_t pk;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(0.0f), "f"(sbs));   // second operand -> low byte
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(pk));
+    s8 = pk & 0xffu;
+    t = __fmul_rn(ts, __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu))));
+}
+
 // Eight elements -> packed e2m1 word (element 2i in the high nibble), exactly as RNE(e2m1)(RN(x / t)), by IEEE
 // division.  Zero decode scale: every element encodes +0 (eager/quantization.py:149-153).
 __device__ __forceinline__ uint32_t quantize8_exact(const float (&f)[8], float t) {
@@ -367,7 +380,17 @@ struct QuantArgs {
     int hi_first;
 };
 
-constexpr int kRing = 6;   // units a thread keeps in flight (16-byte loads), processed two at a time
+// Ring depth and resident blocks per SM (which sets the register budget).  Measured on a B200: 6 units x 3 blocks
+// (78 registers, no spills) is as fast as or faster than 6 x 4 (64 registers with spills in the loop), 4 x 4, 8 x 3 and
+// 10 x 2 at every size from 28 MB to 1.6 GB; all of them end at 5.6-5.75 TB/s on the largest inputs.
+#ifndef CKB_QUANT_RING
+#define CKB_QUANT_RING 6
+#endif
+#ifndef CKB_QUANT_BLOCKS_PER_SM
+#define CKB_QUANT_BLOCKS_PER_SM 3
+#endif
+constexpr int kBlocksPerSM = CKB_QUANT_BLOCKS_PER_SM;   // resident blocks the register budget is set for
+constexpr int kRing = CKB_QUANT_RING;   // units a thread keeps in flight (16-byte loads), processed two at a time
 
 // State of one lane for one segment walk.
 struct LaneCtx {
@@ -520,7 +543,7 @@ __device__ __forceinline__ void walk_interior(const LaneCtx& c, int u_begin, int
 // is selected by lane parity - the caller's addresses differ instead.  Everything is computed as if the block were
 // ordinary (finite, per-tensor scale and amax inside the exact-reciprocal range, or an all-zero block); one vote
 // at the end sends the whole warp to IEEE arithmetic otherwise.  Returns this lane's scale byte in s8.
-template <int DT>
+template <int DT, bool HI_FIRST>
 __device__ __forceinline__ void quantize_pair_xy(const LaneCtx& c, const typename Input<DT>::Raw& raw_x,
                                                  const typename Input<DT>::Raw& raw_y, uint32_t& word_x,
                                                  uint32_t& word_y, uint32_t& s8) {
@@ -528,7 +551,7 @@ __device__ __forceinline__ void quantize_pair_xy(const LaneCtx& c, const typenam
     const float amax = Pairs<DT>::block_amax(raw_x, raw_y);
     const bool ordinary = c.ts_in_range && (amax == 0.0f || (amax >= 0x1p-60f && amax <= 0x1p60f));
     float t;
-    block_scale(amax, c.ts, c.rcp_ts, true, s8, t);   // t is 0 or inside [2^-69, 2^69] for an ordinary block
+    block_scale_ordinary(amax, c.ts, c.rcp_ts, s8, t);   // t is 0 or inside [2^-69, 2^69] for an ordinary block
     const float r = rcp_rn_normal(t);
     const float t_y = __shfl_xor_sync(0xffffffffu, t, 1);
     const float r_y = __shfl_xor_sync(0xffffffffu, r, 1);
@@ -549,7 +572,7 @@ __device__ __forceinline__ void quantize_pair_xy(const LaneCtx& c, const typenam
         word_x = quantize8_exact(gx, t2);
         word_y = quantize8_exact(gy, t2_y);
     }
-    if (!c.hi_first) {
+    if (!HI_FIRST) {
         word_x = swap_nibbles32(word_x);
         word_y = swap_nibbles32(word_y);
     }
@@ -559,7 +582,7 @@ __device__ __forceinline__ void quantize_pair_xy(const LaneCtx& c, const typenam
 // the other way round, by a per-lane offset on the load and store addresses.
 // ROWS_IN = false: some of the warp's rows lie in the zero padding below the input (they are still rows of the
 // output); their lanes skip the loads and quantize zeros.
-template <int DT, bool ROWS_IN>
+template <int DT, bool ROWS_IN, bool HI_FIRST>
 __device__ __forceinline__ void walk_interior_xy(const LaneCtx& c, int u_begin, int u_end) {
     using In = Input<DT>;
     using Raw = typename In::Raw;
@@ -590,7 +613,7 @@ __device__ __forceinline__ void walk_interior_xy(const LaneCtx& c, int u_begin, 
 
     auto consume = [&](int k) {
         uint32_t wx, wy, s8;
-        quantize_pair_xy<DT>(c, raw[k], raw[k + 1], wx, wy, s8);
+        quantize_pair_xy<DT, HI_FIRST>(c, raw[k], raw[k + 1], wx, wy, s8);
         *reinterpret_cast<uint32_t*>(qp_x + k * 32) = wx;
         *reinterpret_cast<uint32_t*>(qp_y + k * 32) = wy;
         const uint32_t sfw = gather_scale_word(s8, sub);
@@ -687,7 +710,7 @@ __device__ __forceinline__ void walk_edge(const LaneCtx& c, int u_begin, int u_e
 // Launch geometry: block (32, WX, WY) with WX * WY = kWarpsPerBlock; warp (wx, wy) of block (bx, by, bz) handles
 // segment bx*WX + wx of row group (bz*65535 + by)*WY + wy, so no thread divides anything.
 template <int DT, bool VEC, int VARIANT>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(const QuantArgs a) {
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, kBlocksPerSM) quantize_nvfp4_kernel(const QuantArgs a) {
     using In = Input<DT>;
     allow_dependent_launch();
     const int lane = threadIdx.x;
@@ -720,8 +743,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 4) quantize_nvfp4_kernel(
     // rows of the warp are r0 + {0,32,64,96}: all inside the input iff the last one is; segments hold whole pairs
     const bool whole_pairs = VEC && (u_end * 64 <= a.cols) && ((u_end - u_begin) % 2 == 0);
     const bool interior = whole_pairs && (band * 128 + d3 + 96 < a.rows);
-    if (interior && VARIANT == 2) walk_interior_xy<DT, true>(c, u_begin, u_end);
-    else if (VARIANT == 2 && whole_pairs && (band * 128 + d3 + 96 < a.prow)) walk_interior_xy<DT, false>(c, u_begin, u_end);
+    if (interior && VARIANT == 2) {
+        if (c.hi_first) walk_interior_xy<DT, true, true>(c, u_begin, u_end);
+        else walk_interior_xy<DT, true, false>(c, u_begin, u_end);
+    } else if (VARIANT == 2 && whole_pairs && (band * 128 + d3 + 96 < a.prow)) {
+        if (c.hi_first) walk_interior_xy<DT, false, true>(c, u_begin, u_end);
+        else walk_interior_xy<DT, false, false>(c, u_begin, u_end);
+    }
     else if (interior) walk_interior<DT, VARIANT>(c, u_begin, u_end);
     else walk_edge<DT, VEC, VARIANT>(c, u_begin, u_end);
 }
@@ -730,9 +758,9 @@ template <int DT>
 int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t stream) {
     if (a.row_groups <= 0 || a.sf_cbg <= 0) return CK_B200_OK;
     // Cut rows into segments of `su` units (even, at least the prefetch ring) so that the blocks fill whole waves
-    // of the 4 blocks an SM holds: among the candidates within 4 % of the best balance take the longest segment
+    // of the kBlocksPerSM blocks an SM holds: among the candidates within 4 % of the best balance take the longest segment
     // (longer walks amortise the per-warp set-up).
-    const int resident = 4 * sms;
+    const int resident = kBlocksPerSM * sms;
     int best_su = kRing, best_wx = 1;
     double best_eff = -1.0;
     for (int pass = 0; pass < 2; ++pass)
