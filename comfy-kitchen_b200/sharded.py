@@ -27,6 +27,30 @@ def shard_rows(n: int, world: int, rank: int, unit: int = 8) -> tuple[int, int]:
     return (rank * u // world) * unit, ((rank + 1) * u // world) * unit
 
 
+def scale_offsets(rows: int, kblocks: int, device=None) -> torch.Tensor:
+    """Byte offset of logical block scale (r, c) inside the 128x4 tiled scale tensor of a [rows, 16*kblocks] operand
+    (``comfy_kitchen/float_utils.py:292-326``), as an int64 [rows, kblocks] tensor."""
+    cbg = (kblocks + 3) // 4
+    r = torch.arange(rows, device=device, dtype=torch.int64).unsqueeze(1)
+    c = torch.arange(kblocks, device=device, dtype=torch.int64).unsqueeze(0)
+    return (((r // 128) * cbg + c // 4) * 32 + r % 32) * 16 + (r % 128) // 32 * 4 + c % 4
+
+
+def untile_scales(sf: torch.Tensor, rows: int, kblocks: int) -> torch.Tensor:
+    """Tiled scale tensor (any shape, uint8 or float8_e4m3fn) -> logical uint8 [rows, kblocks]."""
+    flat = sf.contiguous().view(torch.uint8).reshape(-1)
+    return flat[scale_offsets(rows, kblocks, flat.device)]
+
+
+def tile_scales(logical: torch.Tensor) -> torch.Tensor:
+    """Logical uint8 [rows, kblocks] -> tiled uint8 [roundup(rows,128), roundup(kblocks,4)] with zero padding."""
+    rows, kblocks = logical.shape
+    rp, cp = (rows + 127) // 128 * 128, (kblocks + 3) // 4 * 4
+    out = torch.zeros(rp * cp, dtype=torch.uint8, device=logical.device)
+    out[scale_offsets(rows, kblocks, logical.device).reshape(-1)] = logical.reshape(-1)
+    return out.view(rp, cp)
+
+
 class _DeviceBytes:
     """Lets torch view raw device memory (the CUDA array interface)."""
 
@@ -110,14 +134,14 @@ class ShardedNVFP4Linear:
     """
 
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, *, group=None, ops=None,
-                 input_scale: torch.Tensor | None = None, weight_scale: torch.Tensor | None = None):
+                 input_scale: torch.Tensor | None = None, weight_scale: torch.Tensor | None = None,
+                 world: int | None = None, rank: int | None = None):
         if ops is None:
             from . import ops as _ops
             ops = _ops
         self.ops = ops
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._set_ranks(group, world, rank)
         self.out_features, self.in_features = weight.shape
         self.n0, self.n1 = shard_rows(self.out_features, self.world, self.rank)
         # global per-tensor scale, evaluated in the weight's dtype like TensorCoreNVFP4Layout.quantize does
@@ -133,6 +157,50 @@ class ShardedNVFP4Linear:
         self.qweight = self.qweight[: self.local_rows].contiguous()
         self.bias = None if bias is None else bias[self.n0:self.n1].contiguous()
         self.input_scale = input_scale
+
+    def _set_ranks(self, group, world, rank) -> None:
+        # world / rank given explicitly: a shard prepared outside a process group (tests, offline conversion)
+        if world is not None:
+            self.world, self.rank = int(world), int(rank or 0)
+        else:
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    @classmethod
+    def from_state_dict(cls, state_dict: dict, prefix: str = "", *, group=None, ops=None, world: int | None = None,
+                        rank: int | None = None, device=None) -> "ShardedNVFP4Linear":
+        """This rank's shard of an already quantized linear in the reference's checkpoint format
+        (``samples/nvfp4_linear.py:39-68``: ``weight`` packed uint8 [N, K/2], ``weight_scale`` e4m3 block scales in
+        the 128x4 tiled layout as uint8 or float8, possibly flat, ``weight_scale_2`` the fp32 per-tensor scale,
+        optional ``input_scale`` and ``bias``).  Rows [n0, n1) of the packed weight are sliced; the block scales are
+        per row, so the shard's tiled scale tensor is rebuilt from the rows of the full one (a shard boundary need not
+        be a multiple of 128).  Nothing is re-quantized: the shard is bit-identical to quantizing those rows of the
+        original weight with the global per-tensor scale."""
+        if ops is None:
+            from . import ops as _ops
+            ops = _ops
+        self = cls.__new__(cls)
+        self.ops, self.group = ops, group
+        self._set_ranks(group, world, rank)
+        qweight = state_dict[prefix + "weight"]
+        if qweight.dtype != torch.uint8 or qweight.dim() != 2:
+            raise TypeError("weight must be the packed uint8 [N, K/2] tensor")
+        self.out_features, self.in_features = qweight.shape[0], 2 * qweight.shape[1]
+        if self.in_features % 16:
+            raise ValueError("in_features must be a multiple of 16")
+        self.n0, self.n1 = shard_rows(self.out_features, self.world, self.rank)
+        self.local_rows = self.n1 - self.n0
+        dev = qweight.device if device is None else torch.device(device)
+        kblocks = self.in_features // 16
+        logical = untile_scales(state_dict[prefix + "weight_scale"], self.out_features, kblocks)
+        self.qweight = qweight[self.n0:self.n1].contiguous().to(dev)
+        self.weight_block_scale = tile_scales(logical[self.n0:self.n1].contiguous()).to(dev).view(torch.float8_e4m3fn)
+        self.weight_scale = state_dict[prefix + "weight_scale_2"].to(device=dev, dtype=torch.float32).reshape(())
+        bias = state_dict.get(prefix + "bias")
+        self.bias = None if bias is None else bias[self.n0:self.n1].contiguous().to(dev)
+        inp = state_dict.get(prefix + "input_scale")
+        self.input_scale = None if inp is None else inp.to(device=dev, dtype=torch.float32).reshape(())
+        return self
 
     def local(self, x: torch.Tensor) -> torch.Tensor:
         """This rank's [M, n1-n0] block of the output."""
