@@ -11,12 +11,13 @@ The kernels live in ``libck_b200.so`` (C ABI in ``include/ck_b200.h``); there is
 from . import _lib
 from .backend import install, uninstall
 from .build import build_library
-from .ops import (dequantize_nvfp4, dynamic_scale_nvfp4, launches, quantize_nvfp4, read_device_status,
+from .ops import (dequantize_mxfp8, dequantize_nvfp4, dynamic_scale_nvfp4, launches, linear_nvfp4, quantize_mxfp8,
+                  quantize_nvfp4, read_device_status, scaled_mm_mxfp8,
                   scaled_mm_nvfp4, set_tuning)
 from .linear import NVFP4Linear
 from .sharded import PeerGroup, PeerMemory, ShardedNVFP4Linear, shard_rows
 
 __all__ = [
-    "quantize_nvfp4", "dequantize_nvfp4", "scaled_mm_nvfp4", "dynamic_scale_nvfp4", "install", "uninstall",
+    "quantize_nvfp4", "dequantize_nvfp4", "scaled_mm_nvfp4", "dynamic_scale_nvfp4", "linear_nvfp4", "quantize_mxfp8", "dequantize_mxfp8", "scaled_mm_mxfp8", "install", "uninstall",
     "build_library", "NVFP4Linear", "PeerGroup", "PeerMemory", "ShardedNVFP4Linear", "shard_rows", "set_tuning", "launches", "read_device_status",
 ]

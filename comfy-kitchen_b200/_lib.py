@@ -23,6 +23,11 @@ EXPORTED_SYMBOLS = (
     "ck_b200_peer_close",
     "ck_b200_peer_free",
     "ck_b200_dynamic_scale_nvfp4",
+    "ck_b200_quantize_mxfp8",
+    "ck_b200_dequantize_mxfp8",
+    "ck_b200_scaled_mm_mxfp8",
+    "ck_b200_linear_nvfp4",
+    "ck_b200_linear_nvfp4_workspace_bytes",
     "ck_b200_last_error",
     "ck_b200_query",
     "ck_b200_read_device_status",
@@ -69,6 +74,16 @@ def load() -> ctypes.CDLL:
     L.ck_b200_peer_close.restype = i32
     L.ck_b200_peer_free.argtypes = [vp]
     L.ck_b200_peer_free.restype = i32
+    L.ck_b200_linear_nvfp4.argtypes = [vp, i32, i64, i64, vp, vp, vp, vp, i64, vp, i32, vp, i32, vp, sz, vp]
+    L.ck_b200_linear_nvfp4.restype = i32
+    L.ck_b200_linear_nvfp4_workspace_bytes.argtypes = [i64, i64]
+    L.ck_b200_linear_nvfp4_workspace_bytes.restype = i64
+    L.ck_b200_quantize_mxfp8.argtypes = [vp, i32, vp, vp, i64, i64, i32, vp]
+    L.ck_b200_quantize_mxfp8.restype = i32
+    L.ck_b200_dequantize_mxfp8.argtypes = [vp, vp, vp, i32, i64, i64, vp]
+    L.ck_b200_dequantize_mxfp8.restype = i32
+    L.ck_b200_scaled_mm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i32, vp, i32, i64, i64, i64, vp, sz, vp]
+    L.ck_b200_scaled_mm_mxfp8.restype = i32
     L.ck_b200_dynamic_scale_nvfp4.argtypes = [vp, i32, i64, vp, vp]
     L.ck_b200_dynamic_scale_nvfp4.restype = i32
     L.ck_b200_last_error.argtypes = []

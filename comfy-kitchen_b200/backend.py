@@ -72,8 +72,47 @@ def _call_rule_scaled_mm(ValidationResult):
     return rule
 
 
+def _call_rule_quantize_mx(ValidationResult):
+    def rule(kwargs):
+        x = kwargs.get("x")
+        if isinstance(x, torch.Tensor):
+            if not x.is_contiguous():
+                return ValidationResult.fail("x", "must be contiguous")
+            if not kwargs.get("pad_32x", False) and (x.dim() != 2 or x.shape[0] % 32 or x.shape[1] % 32):
+                return ValidationResult.fail("x", "rows and cols must be divisible by 32 unless pad_32x")
+        return ValidationResult.ok()
+    return rule
+
+
+def _call_rule_mx_operands(ValidationResult):
+    """dequantize_mxfp8 (qx, block_scales) and scaled_mm_mxfp8 (a, b, block_scale_a, block_scale_b)."""
+    def rule(kwargs):
+        pairs = [(kwargs.get("qx"), kwargs.get("block_scales"), "block_scales"),
+                 (kwargs.get("a"), kwargs.get("block_scale_a"), "block_scale_a"),
+                 (kwargs.get("b"), kwargs.get("block_scale_b"), "block_scale_b")]
+        for q, sf, name in pairs:
+            if not isinstance(q, torch.Tensor):
+                continue
+            if q.dim() != 2 or not q.is_contiguous() or q.shape[1] % 32:
+                return ValidationResult.fail(name, "data must be contiguous 2D with K divisible by 32")
+            if isinstance(sf, torch.Tensor) and (tuple(sf.shape) != (ops.roundup(q.shape[0], 128), ops.roundup(q.shape[1] // 32, 4))
+                                                or not sf.is_contiguous() or sf.device != q.device):
+                return ValidationResult.fail(name, "wrong shape, layout or device")
+        a, b, bias = kwargs.get("a"), kwargs.get("b"), kwargs.get("bias")
+        if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor):
+            if a.shape[1] != b.shape[1]:
+                return ValidationResult.fail("b", "K of a and b differ")
+            if b.shape[0] % 8:
+                return ValidationResult.fail("b", "N must be divisible by 8")
+            if isinstance(bias, torch.Tensor) and bias.numel() > 0 and (
+                    bias.dtype not in (torch.float16, torch.bfloat16) or bias.numel() != b.shape[0] or bias.device != a.device):
+                return ValidationResult.fail("bias", "must be an fp16/bf16 [N] tensor on the operands' device")
+        return ValidationResult.ok()
+    return rule
+
+
 def build_constraints():
-    """{function name: FunctionConstraints} for the three operators of this backend."""
+    """{function name: FunctionConstraints} for the operators of this backend (NVFP4 and MXFP8)."""
     from comfy_kitchen.constraints import (DivisibleBy, ExactDims, FunctionConstraints, ParamConstraint,
                                            ValidationResult)
     cuda = frozenset({"cuda"})
@@ -104,6 +143,25 @@ def build_constraints():
                     "out_dtype": ParamConstraint(dtypes=frozenset({torch.float16, torch.bfloat16}))},
             default_devices=cuda, min_compute_capability=(10, 0),
             call_rules=(_call_rule_scaled_mm(ValidationResult),)),
+        # the MXFP8 sibling path (comfy_kitchen/backends/eager/__init__.py:528-567)
+        "quantize_mxfp8": FunctionConstraints(
+            params={"x": ParamConstraint(dtypes=floats, shape_rules=(ExactDims(2),))},
+            default_devices=cuda, min_compute_capability=(10, 0),
+            call_rules=(_call_rule_quantize_mx(ValidationResult),)),
+        "dequantize_mxfp8": FunctionConstraints(
+            params={"qx": ParamConstraint(dtypes=e4m3, shape_rules=(ExactDims(2),)),
+                    "block_scales": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "output_type": ParamConstraint(dtypes=floats)},
+            default_devices=cuda, min_compute_capability=(10, 0),
+            call_rules=(_call_rule_mx_operands(ValidationResult),)),
+        "scaled_mm_mxfp8": FunctionConstraints(
+            params={"a": ParamConstraint(dtypes=e4m3, shape_rules=(ExactDims(2),)),
+                    "b": ParamConstraint(dtypes=e4m3, shape_rules=(ExactDims(2),)),
+                    "block_scale_a": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "block_scale_b": ParamConstraint(dtypes=frozenset({torch.float8_e8m0fnu})),
+                    "out_dtype": ParamConstraint(dtypes=floats)},
+            default_devices=cuda, min_compute_capability=(10, 0),
+            call_rules=(_call_rule_mx_operands(ValidationResult),)),
     }
 
 
@@ -115,6 +173,9 @@ def backend_module() -> types.ModuleType:
     mod.quantize_nvfp4 = ops.quantize_nvfp4
     mod.dequantize_nvfp4 = ops.dequantize_nvfp4
     mod.scaled_mm_nvfp4 = ops.scaled_mm_nvfp4
+    mod.quantize_mxfp8 = ops.quantize_mxfp8
+    mod.dequantize_mxfp8 = ops.dequantize_mxfp8
+    mod.scaled_mm_mxfp8 = ops.scaled_mm_mxfp8
     return mod
 
 

@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libck_b200.so")
-SOURCES = ["abi.cu", "quantize_nvfp4.cu", "gemm_nvfp4_sm100.cu"]
+SOURCES = ["abi.cu", "quantize_nvfp4.cu", "gemm_nvfp4_sm100.cu", "mxfp8.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -140,4 +140,58 @@ int ck_b200_peer_free(void* ptr) {
     return CK_B200_OK;
 }
 
+// ---- the whole linear in one call -------------------------------------------------------------------------------
+
+namespace {
+struct LinearPlan {
+    int64_t prow;          // activation rows after padding to 16
+    size_t scale_off, q_off, sf_off, end;   // byte offsets inside the workspace
+};
+LinearPlan plan_linear(int64_t M, int64_t K) {
+    LinearPlan p;
+    p.prow = ckb::round_up64(M, 16);
+    p.scale_off = 0;
+    p.q_off = 256;
+    p.sf_off = p.q_off + (size_t)ckb::round_up64(p.prow * (K / 2), 256);
+    p.end = p.sf_off + (size_t)ckb::round_up64(ckb::round_up64(p.prow, 128) * ckb::round_up64(K / 16, 4), 256);
+    return p;
+}
+}  // namespace
+
+int64_t ck_b200_linear_nvfp4_workspace_bytes(int64_t M, int64_t K) {
+    if (M < 0 || K < 0 || K % 32 != 0) return -1;
+    return (int64_t)plan_linear(M, K).end;
+}
+
+int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* input_scale_dev_or_null,
+                         const void* w_q_dev, const void* w_sf_dev, const float* w_scale_dev, int64_t N,
+                         const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype,
+                         void* workspace_dev, size_t workspace_bytes, void* stream) {
+    if (M < 0 || N < 0 || K < 0 || K % 32 != 0)
+        return ckb::fail(CK_B200_ERR_INVALID_ARGUMENT, "linear_nvfp4: K = %lld must be a non-negative multiple of 32",
+                         (long long)K);
+    if (M == 0 || N == 0) return CK_B200_OK;
+    const LinearPlan p = plan_linear(M, K);
+    if (!workspace_dev || ((uintptr_t)workspace_dev & 255) || workspace_bytes < p.end)
+        return ckb::fail(CK_B200_ERR_INVALID_ARGUMENT,
+                         "linear_nvfp4: workspace must be 256-byte aligned and hold %lld bytes "
+                         "(ck_b200_linear_nvfp4_workspace_bytes)", (long long)p.end);
+    char* ws = (char*)workspace_dev;
+    const float* ts_x = input_scale_dev_or_null;
+    if (!ts_x) {
+        float* dyn = (float*)(ws + p.scale_off);
+        if (int rc = ck_b200_dynamic_scale_nvfp4(x_dev, x_dtype, M * K, dyn, stream)) return rc;
+        ts_x = dyn;
+    }
+    void* qx = ws + p.q_off;
+    void* sfx = ws + p.sf_off;
+    if (int rc = ck_b200_quantize_nvfp4(x_dev, x_dtype, ts_x, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1, stream))
+        return rc;
+    // what is left of the workspace serves the split-K reduction of small-M problems
+    const size_t rest = workspace_bytes - p.end;
+    return ck_b200_scaled_mm_nvfp4(qx, sfx, w_q_dev, w_sf_dev, ts_x, w_scale_dev, nullptr, bias_dev_or_null, bias_dtype,
+                                   out_dev, out_dtype, M, N, K, rest >= (1u << 20) ? ws + p.end : nullptr,
+                                   rest >= (1u << 20) ? rest : 0, stream);
+}
+
 }  // extern "C"

@@ -104,6 +104,9 @@ struct Cfg {
     // UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
     static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (0u << 23) |
                                        ((uint32_t)(BM >> 4) << 24);
+    // kind::mxf8f6f4.block_scale: A,B = e4m3 (format 0), UE8M0 scales (bit 23); the byte of the four-byte scale cell
+    // that an instruction uses is chosen per instruction: b_sf_id at bit 4, a_sf_id at bit 29
+    static constexpr uint32_t kIdescMx = ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------
@@ -178,6 +181,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_mx(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
         : "memory");
 }
@@ -288,11 +299,15 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int tile, int& tm
 
 // ---- kernel -----------------------------------------------------------------------------------------
 
-template <int BN, bool DBG>
+// FMT 0: NVFP4 (packed e2m1, e4m3 scales per 16 elements, 256 elements of K per stage).
+// FMT 1: MXFP8 (e4m3 bytes, e8m0 scales per 32 elements, 128 elements of K per stage): the same 128-byte operand rows
+// and 32-byte steps per instruction, but one scale chunk per stage, whose four bytes per row serve the four instructions.
+template <int BN, bool DBG, int FMT = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
     using C = Cfg<BN>;
+    constexpr bool MX = (FMT == 1);
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -365,18 +380,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (!ok) break;
                 const uint32_t st = smem_u32(smem) + stage * C::kStageBytes;
                 const uint32_t bar = smem_u32(&full_bar[0]) + stage * 8;
-                const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                const int chunk0 = MX ? kb : kb * CHUNKS;   // first scale chunk of this stage
+                const int nchunk = MX ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
                 const uint32_t sf_bytes = nchunk * SF_CHUNK_BYTES;
                 if (elect_one()) {
                     mbar_expect_tx(bar, C::kABytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
                     tma_load_2d(st, &tmap_a, kb * BK_BYTES, tm * BM, bar);
                     tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * BN, bar);
-                    bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)kb * CHUNKS * SF_CHUNK_BYTES, sf_bytes, bar);
+                    bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)chunk0 * SF_CHUNK_BYTES, sf_bytes, bar);
 #pragma unroll
                     for (int b = 0; b < C::kBands; ++b)
                         if (b < sfb_present)
                             bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes,
-                                      sfb_src + ((int64_t)b * g.sf_cbg + kb * CHUNKS) * SF_CHUNK_BYTES, sf_bytes, bar);
+                                      sfb_src + ((int64_t)b * g.sf_cbg + chunk0) * SF_CHUNK_BYTES, sf_bytes, bar);
                 }
                 __syncwarp();
                 if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -420,7 +436,24 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const uint32_t sfa_lo = st_enc + ((C::kABytes + C::kBBytes) >> 4);
                 const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
                 const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
-                if (elect_one()) {
+                if (MX) {
+                    if (elect_one()) {
+                        // one chunk per 128-row band per stage: cell (row, column) holds the scales of the stage's four
+                        // 32-element blocks, one byte per instruction; the two regions alternate between stages
+                        const uint32_t region = sf_t0 + (uint32_t)(kb & 1) * C::kSfRegionCols;
+                        const uint32_t sfa_t = region, sfb_t = region + C::kSfaColsHalf;
+                        tc_cp_sf(sfa_t, desc64(sfa_lo, kSfDescHi));
+#pragma unroll
+                        for (int b = 0; b < C::kBands; ++b)
+                            tc_cp_sf(sfb_t + 4 * b, desc64(sfb_lo + (b * C::kSfaBytes) / 16, kSfDescHi));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_mma_mx(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
+                                      C::kIdescMx | ((uint32_t)j << 29) | ((uint32_t)j << 4), sfa_t, sfb_t,
+                                      (j != 0 || kb != kb0) ? 1u : 0u);
+                        tc_commit(smem_u32(&empty_bar[0]) + stage * 8);
+                    }
+                } else if (elect_one()) {
                     // scale factors of step j go to region j/2 (the two regions alternate, so a copy never
                     // overwrites scales that the MMAs issued just before it still read)
 #pragma unroll
@@ -1167,19 +1200,20 @@ int choose_splits(int n_tiles, int k_iters, int sms, int64_t M, int64_t N, size_
     return s < 1 ? 1 : s;
 }
 
-template <int BN>
+template <int BN, int FMT = 0>
 int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream, float* scratch,
                 size_t scratch_bytes) {
     using C = Cfg<BN>;
-    auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true> : gemm_nvfp4_kernel<BN, false>;
+    auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true, FMT> : gemm_nvfp4_kernel<BN, false, FMT>;
+    const int64_t row_bytes = FMT == 1 ? K : K / 2;   // e4m3 bytes or packed e2m1 nibbles
     // opting in to large dynamic shared memory is per function and per device; doing it on every call is cheap
     cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (attr_err != cudaSuccess)
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
                     cudaGetErrorString(attr_err));
     CUtensorMap ma, mb, mo;
-    if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM)) return rc;
-    if (int rc = make_operand_map(&mb, b, g.N, K / 2, BN)) return rc;
+    if (int rc = make_operand_map(&ma, a, g.M, row_bytes, BM)) return rc;
+    if (int rc = make_operand_map(&mb, b, g.N, row_bytes, BN)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
         if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
@@ -1189,7 +1223,7 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     g.m_tiles = (int)ceil_div64(g.M, BM);
     g.n_tiles = (int)ceil_div64(g.N, BN);
     // as many tile rows per group as keep the group's A rows (with room for B and the output) inside the 126 MB L2
-    const int64_t row_block_bytes = (int64_t)BM * (K / 2);
+    const int64_t row_block_bytes = (int64_t)BM * row_bytes;
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 8) group = 8;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
@@ -1365,6 +1399,82 @@ extern "C" int ck_b200_peer_barrier(void* const* flag_ptrs, int world, int rank,
     g_launches.fetch_add(1);
     CKB_CUDA_OK(cudaGetLastError());
     return CK_B200_OK;
+}
+
+// ---- MXFP8 GEMM ----------------------------------------------------------------------------------------
+
+namespace {
+static __device__ float g_unit_alpha = 1.0f;   // MXFP8 has no per-tensor scales: the epilogue multiplies by this
+
+int unit_alpha_address(const float** out) {
+    static std::mutex mu;
+    static void* cache[64] = {nullptr};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_unit_alpha);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(CK_B200_ERR_CUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        cache[dev] = p;
+    }
+    *out = reinterpret_cast<const float*>(cache[dev]);
+    return CK_B200_OK;
+}
+}  // namespace
+
+extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                                       const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype,
+                                       int64_t M, int64_t N, int64_t K, void* workspace_dev, size_t workspace_bytes,
+                                       void* stream) {
+    int sms = 0;
+    if (int rc = check_device(&sms)) return rc;
+    if (!a_dev || !sfa_dev || !b_dev || !sfb_dev || !out_dev)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: null pointer");
+    if (M < 0 || N < 0 || K < 0 || M > 0x7fffff00ll || N > 0x7fffff00ll || K > 0x7fffff00ll)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: bad shape");
+    if (K % 32 != 0 || N % 8 != 0)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: K = %lld must be a multiple of 32 and N = %lld of 8",
+                    (long long)K, (long long)N);
+    if (out_dtype < 0 || out_dtype > 2 || (bias_dev_or_null && (bias_dtype < 0 || bias_dtype > 2)))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: bad dtype code");
+    if (((uintptr_t)a_dev & 15) || ((uintptr_t)b_dev & 15) || ((uintptr_t)sfa_dev & 15) || ((uintptr_t)sfb_dev & 15) ||
+        ((uintptr_t)out_dev & 15) || ((uintptr_t)workspace_dev & 15))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: operands, scales, output and workspace must be 16-byte aligned");
+    if (M == 0 || N == 0) return CK_B200_OK;
+    if (K == 0) return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_mxfp8: K must be positive");
+    const float* one = nullptr;
+    if (int rc = unit_alpha_address(&one)) return rc;
+    GemmArgs g;
+    g.sfa = (const uint8_t*)sfa_dev;
+    g.sfb = (const uint8_t*)sfb_dev;
+    g.tsa = g.tsb = nullptr;
+    g.alpha = one;
+    g.bias = bias_dev_or_null;
+    g.out = out_dev;
+    g.bias_dtype = bias_dtype;
+    g.out_dtype = out_dtype;
+    g.M = (int)M;
+    g.N = (int)N;
+    g.sf_cbg = (int)ceil_div64(K, 128);    // one 512-byte chunk = 128 rows x 4 blocks of 32 elements
+    g.sfb_bands = (int)ceil_div64(N, 128);
+    g.k_iters = (int)ceil_div64(K, 128);   // 128 elements = 128 bytes of K per stage
+    g.m_tiles = g.n_tiles = 0;
+    g.splits = 1;
+    g.k_per_split = g.k_iters;
+    g.partial = nullptr;
+    g.raster_group = 1;
+    g.tma_store = 0;
+    g.ld_out = N;
+    g.n_peers = 0;
+    for (int p = 0; p < 7; ++p) g.peer_out[p] = nullptr;
+    g.debug = g_gemm_debug.load();
+    cudaStream_t s = (cudaStream_t)stream;
+    float* scratch = (float*)workspace_dev;
+    if (N > 128 && M > 128) return launch_gemm<256, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    return launch_gemm<128, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
 }
 
 // ---- entry point with built-in scratch --------------------------------------------------------------

@@ -77,13 +77,29 @@ class NVFP4Linear(nn.Module):
         x2 = x.reshape(-1, self.in_features)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        out_dtype = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else self.compute_dtype
+        bias = self.bias
+        if bias is not None and bias.shape[0] != self.weight.shape[0]:   # out_features padded to 16 rows
+            bias = torch.nn.functional.pad(bias, (0, self.weight.shape[0] - bias.shape[0]))
+        # one library call: activation scale, quantization of x (rows padded to 16) and the GEMM.  The quantized
+        # activation sits in a per-device workspace, so calls on one device must be ordered on one stream.
+        y = ops.linear_nvfp4(x2, self.weight, self.weight_scale.view(torch.float8_e4m3fn), self.weight_scale_2,
+                             input_scale=self.input_scale, bias=bias, out_dtype=out_dtype)
+        return y[:, : self.out_features].reshape(*lead, self.out_features)
+
+    def forward_unfused(self, x: torch.Tensor) -> torch.Tensor:
+        """The same result through the three operators of the reference interface, one call each."""
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
         m = x2.shape[0]
         scale = self.input_scale if self.input_scale is not None else ops.dynamic_scale_nvfp4(x2)
         pad = m % 16 != 0 or self.in_features % 16 != 0
         qx, sfx = ops.quantize_nvfp4(x2, scale, pad_16x=pad)
         out_dtype = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else self.compute_dtype
         bias = self.bias
-        if bias is not None and bias.shape[0] != self.weight.shape[0]:   # out_features padded to 16 rows
+        if bias is not None and bias.shape[0] != self.weight.shape[0]:
             bias = torch.nn.functional.pad(bias, (0, self.weight.shape[0] - bias.shape[0]))
         y = ops.scaled_mm_nvfp4(qx, self.weight, scale, self.weight_scale_2, sfx,
                                 self.weight_scale.view(torch.float8_e4m3fn), bias=bias, out_dtype=out_dtype)

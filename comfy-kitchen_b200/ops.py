@@ -255,6 +255,133 @@ def peer_free(ptr: int, device: torch.device) -> None:
         _lib.check(_lib.load().ck_b200_peer_free(ptr), "peer_free")
 
 
+# ---- MXFP8: same interface as the reference operators (comfy_kitchen/backends/cuda/__init__.py:1689-1722,
+# comfy_kitchen/backends/eager/quantization.py:319-405) ----------------------------------------------------------
+
+def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """x [M, K] -> (float8_e4m3fn [Mp, Kp], float8_e8m0fnu block scales [roundup(Mp,128), roundup(Kp/32,4)] tiled)."""
+    x = _plain(x)
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype not in DTYPE_TO_CODE:
+        raise TypeError("quantize_mxfp8 needs a 2D float32/float16/bfloat16 tensor")
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    rows, cols = x.shape
+    if pad_32x:
+        prow, pcol = roundup(rows, 32), roundup(cols, 32)
+    else:
+        prow, pcol = rows, cols
+        assert rows % 32 == 0, f"num_rows must be divisible by 32, got {rows}"
+        assert cols % 32 == 0, f"num_cols must be divisible by 32, got {cols}"
+    with torch.cuda.device(x.device):
+        q = torch.empty((prow, pcol), dtype=torch.uint8, device=x.device)
+        sf = torch.empty((roundup(prow, 128), roundup(pcol // 32, 4)), dtype=torch.uint8, device=x.device)
+        rc = _lib.load().ck_b200_quantize_mxfp8(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(q), _ptr(sf), rows, cols,
+                                                int(pad_32x), _stream(x.device))
+    _lib.check(rc, "quantize_mxfp8")
+    return q.view(torch.float8_e4m3fn), sf.view(torch.float8_e8m0fnu)
+
+
+def dequantize_mxfp8(qx: torch.Tensor, block_scales: torch.Tensor, output_type: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    qx, block_scales = _plain(qx), _plain(block_scales)
+    _require_cuda(qx, "qx")
+    if output_type not in DTYPE_TO_CODE:
+        raise TypeError(f"dequantize_mxfp8: unsupported output type {output_type}")
+    assert qx.dim() == 2 and qx.is_contiguous() and block_scales.is_contiguous()
+    rows, cols = qx.shape
+    assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 32, 4)), "Invalid scale shape"
+    with torch.cuda.device(qx.device):
+        out = torch.empty((rows, cols), dtype=output_type, device=qx.device)
+        rc = _lib.load().ck_b200_dequantize_mxfp8(_ptr(qx), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type],
+                                                  rows, cols, _stream(qx.device))
+    _lib.check(rc, "dequantize_mxfp8")
+    return out
+
+
+def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
+                    bias: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """[M, K] x [N, K]^T e4m3 with e8m0 scales per 32 elements -> [M, N] in ``out_dtype`` (default bf16)."""
+    a, b = _plain(a), _plain(b)
+    block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
+    _require_cuda(a, "a")
+    if out_dtype is None:
+        out_dtype = torch.bfloat16
+    if out_dtype not in DTYPE_TO_CODE:
+        raise TypeError(f"scaled_mm_mxfp8: unsupported out_dtype {out_dtype}")
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], "Matrix dimensions do not match"
+    assert a.element_size() == 1 and b.element_size() == 1 and a.is_contiguous() and b.is_contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    assert k % 32 == 0 and n % 8 == 0, "K must be a multiple of 32 and N of 8"
+    sk = roundup(k // 32, 4)
+    assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    assert tuple(block_scale_b.shape) == (roundup(n, 128), sk), "Invalid B scale shape"
+    bias_code = 2
+    if bias is not None and bias.numel() > 0:
+        bias = _plain(bias)
+        assert bias.numel() == n and bias.is_contiguous() and bias.dtype in (torch.float16, torch.bfloat16)
+        bias_code = DTYPE_TO_CODE[bias.dtype]
+    else:
+        bias = None
+    with torch.cuda.device(a.device):
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+        if out.numel() == 0:
+            return out
+        ws = _workspace(a.device) if m <= 128 else None
+        rc = _lib.load().ck_b200_scaled_mm_mxfp8(_ptr(a), _ptr(block_scale_a), _ptr(b), _ptr(block_scale_b), _ptr(bias),
+                                                 bias_code, _ptr(out), DTYPE_TO_CODE[out_dtype], m, n, k, _ptr(ws),
+                                                 0 if ws is None else ws.numel(), _stream(a.device))
+    _lib.check(rc, "scaled_mm_mxfp8")
+    return out
+
+
+_LINEAR_WS: dict[int, torch.Tensor] = {}
+
+
+def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: torch.Tensor, weight_scale: torch.Tensor,
+                 input_scale: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y[M, N] = x[M, K] @ W^T + bias with W resident in NVFP4: the activation scale (``input_scale`` or the layout's
+    dynamic one), the quantization of x and the GEMM are enqueued by one library call, with the quantized activation
+    in a per-device workspace that grows on demand.  Same arithmetic as dynamic_scale_nvfp4 -> quantize_nvfp4(pad_16x)
+    -> scaled_mm_nvfp4, so results are bit-identical to calling those three."""
+    x = _plain(x)
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype not in DTYPE_TO_CODE:
+        raise TypeError("linear_nvfp4 needs a 2D float32/float16/bfloat16 activation")
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    qweight, weight_block_scale = _plain(qweight), _plain(weight_block_scale)
+    m, k = x.shape
+    n = qweight.shape[0]
+    assert qweight.dtype == torch.uint8 and qweight.shape[1] * 2 == k and qweight.is_contiguous()
+    assert tuple(weight_block_scale.shape) == (roundup(n, 128), roundup(k // 16, 4)), "Invalid weight scale shape"
+    if out_dtype is None:
+        out_dtype = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16
+    bias_code = 2
+    if bias is not None:
+        bias = _plain(bias)
+        assert bias.numel() == n and bias.is_contiguous() and bias.dtype in (torch.float16, torch.bfloat16)
+        bias_code = DTYPE_TO_CODE[bias.dtype]
+    L = _lib.load()
+    need = L.ck_b200_linear_nvfp4_workspace_bytes(m, k)
+    if need < 0:
+        raise RuntimeError(f"linear_nvfp4: K = {k} must be a multiple of 32")
+    need += _WORKSPACE_BYTES if m <= 128 else 0
+    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    ws = _LINEAR_WS.get(idx)
+    with torch.cuda.device(x.device):
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 64 << 20), dtype=torch.uint8, device=x.device)
+            _LINEAR_WS[idx] = ws
+        w_ts = _scale_on(x.device, weight_scale)
+        in_ts = None if input_scale is None else _scale_on(x.device, input_scale)
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        rc = L.ck_b200_linear_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], m, k, _ptr(in_ts), _ptr(qweight),
+                                    _ptr(weight_block_scale), _ptr(w_ts), n, _ptr(bias), bias_code, _ptr(out),
+                                    DTYPE_TO_CODE[out_dtype], _ptr(ws), ws.numel(), _stream(x.device))
+    _lib.check(rc, "linear_nvfp4")
+    return out
+
+
 def dynamic_scale_nvfp4(x: torch.Tensor) -> torch.Tensor:
     """amax(|x|)/(448*6) evaluated in x's dtype and returned as a float32 scalar tensor on x's device: the
     per-tensor scale ``TensorCoreNVFP4Layout.quantize`` computes when none is given

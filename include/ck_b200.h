@@ -148,6 +148,45 @@ int ck_b200_peer_close(void* ptr);
 int ck_b200_peer_free(void* ptr);
 
 /*
+ * The whole NVFP4 linear of the reference layer (samples/nvfp4_linear.py:77-80 through
+ * comfy_kitchen/tensor/nvfp4.py:53-84,212-260) in one call: per-tensor activation scale (given, or derived from x like
+ * the layout does), quantize_nvfp4 of x with rows padded to 16, scaled_mm_nvfp4 with the resident quantized weight,
+ * bias and output rounding.  Enqueues three to five kernels; the quantized activation lives in the caller's workspace.
+ *
+ *   x_dev [M, K] of dtype code x_dtype, K % 32 == 0;  input_scale_dev_or_null: one float32, or NULL for the dynamic scale
+ *   w_q_dev [N, K/2], w_sf_dev tiled e4m3 [roundup(N,128), roundup(K/16,4)], w_scale_dev one float32, N % 8 == 0
+ *   out_dev [M, N] of dtype code out_dtype;  bias_dev_or_null [N]
+ *   workspace_dev: 256-byte aligned, at least ck_b200_linear_nvfp4_workspace_bytes(M, K) bytes; anything beyond that
+ *   (1 MiB or more) is used for the split-K reduction when M <= 128
+ */
+int64_t ck_b200_linear_nvfp4_workspace_bytes(int64_t M, int64_t K);
+int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* input_scale_dev_or_null,
+                         const void* w_q_dev, const void* w_sf_dev, const float* w_scale_dev, int64_t N,
+                         const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype,
+                         void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/*
+ * MXFP8, the sibling format of the same path: e4m3 data with one power-of-two (e8m0) scale per 32 elements, scales in
+ * the same 128x4 tiled layout.  Replace launch_quantize_mxfp8_kernel (comfy_kitchen/backends/cuda/ops/quantize_mxfp8.cu:40-139)
+ * and the eager dequantize_mxfp8 / scaled_mm_mxfp8 (comfy_kitchen/backends/eager/quantization.py:260-405; the
+ * reference has no CUDA GEMM for this format, its eager path calls cuBLASLt through torch).
+ *
+ *   quantize:   x_dev [rows, cols] (dtype code 0/1/2) -> q_out_dev e4m3 bytes [prow, pcol] and sf_out_dev e8m0 bytes
+ *               [roundup(prow,128), roundup(pcol/32,4)] tiled, prow/pcol = rows/cols rounded up to 32 when pad_32x,
+ *               otherwise rows and cols must be multiples of 32; the kernel writes all padding itself
+ *   dequantize: out_dev [rows, cols] of dtype code out_dtype = out(e4m3 * 2^(e-127)), cols % 32 == 0
+ *   scaled_mm:  out[M,N] = out_dtype(A . B^T + bias), A [M,K] and B [N,K] e4m3 bytes, fp32 accumulation;
+ *               K % 32 == 0, N % 8 == 0; workspace as for ck_b200_scaled_mm_nvfp4 (split-K for M <= 128)
+ */
+int ck_b200_quantize_mxfp8(const void* x_dev, int x_dtype, void* q_out_dev, void* sf_out_dev, int64_t rows, int64_t cols,
+                           int pad_32x, void* stream);
+int ck_b200_dequantize_mxfp8(const void* q_dev, const void* sf_dev, void* out_dev, int out_dtype, int64_t rows,
+                             int64_t cols, void* stream);
+int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                            const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M,
+                            int64_t N, int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/*
  * amax(|x|) / (448*6) computed in the input dtype and widened to float32, the per-tensor scale
  * TensorCoreNVFP4Layout.quantize derives when the caller gives none (comfy_kitchen/tensor/nvfp4.py:66-71).
  * scale_out_dev receives one float32.  Two launches on `stream` (reduce, finalise); no host sync.

@@ -319,6 +319,84 @@ float nvfp4_oracle_dynamic_scale(const void* x, int dtype, int64_t n) {
     return round_to_dtype(amax / 2688.0f, dtype);
 }
 
+/* ---- MXFP8: block 32, power-of-two (e8m0) block scales, e4m3 data ---------------------------------
+ * Restates comfy_kitchen/backends/eager/quantization.py:260-364 (quantize_mxfp8, dequantize_mxfp8) and
+ * e8m0_to_f32 (comfy_kitchen/float_utils.py:376-382).  One deliberate difference, stated here and checked by
+ * the golden vectors: the reference takes ceil(log2(amax/448)) with a float32 log2, which rounds a quotient
+ * that lies within ~2.6e-6 above a power of two down onto it (one exponent lower); this restatement takes the
+ * exact ceiling.  The reference's own tests allow +-1 on the exponent between its backends
+ * (tests/test_qdq.py:431-438); on bf16 and fp16 inputs the two agree always (amax/448 cannot come that close).
+ */
+
+/* biased e8m0 exponent of a block with the given amax (> 0) */
+static inline int mxfp8_biased_exponent(float amax) {
+    float need = amax / 448.0f;
+    const float min_scale = bits_f32(0x00400000u); /* 2^-127 */
+    if (need < min_scale) need = min_scale;
+    int ex;
+    const float fr = frexpf(need, &ex);            /* need = fr * 2^ex, fr in [0.5, 1) */
+    int ce = (fr == 0.5f) ? ex - 1 : ex;           /* exact ceil(log2(need)) */
+    int biased = ce + 127;
+    if (biased < 0) biased = 0;
+    if (biased > 254) biased = 254;
+    return biased;
+}
+
+int mxfp8_oracle_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int pad_32x, uint8_t* q_out,
+                          uint8_t* sf_out) {
+    const int64_t prow = pad_32x ? round_up(rows, 32) : rows;
+    const int64_t pcol = pad_32x ? round_up(cols, 32) : cols;
+    if (pcol % 32 != 0) return 1;
+    const int64_t nblk = pcol / 32;
+    const int64_t sf_rows = round_up(prow, 128), sf_cols = round_up(nblk, 4);
+    memset(sf_out, 0, (size_t)(sf_rows * sf_cols));
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < prow; ++r) {
+        for (int64_t b = 0; b < nblk; ++b) {
+            float v[32];
+            float amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                const int64_t c = b * 32 + i;
+                v[i] = (r < rows && c < cols) ? load_as_f32(x, dtype, r * cols + c) : 0.0f;
+                const float a = fabsf(v[i]);
+                if (a > amax) amax = a;
+            }
+            uint8_t* q = q_out + r * pcol + b * 32;
+            if (amax == 0.0f) {                       /* zero block: scale byte 0, data +0 */
+                memset(q, 0, 32);
+                continue;
+            }
+            const int biased = mxfp8_biased_exponent(amax);
+            sf_out[swizzled_sf_offset(r, b, sf_cols)] = (uint8_t)biased;
+            /* e8m0_to_f32 maps a biased exponent of 0 to 0.0, not 2^-127: the division below then yields
+             * +-inf (clamped to +-448) and, for zero elements, the default NaN (sign set on the CPU) */
+            const float scale = biased == 0 ? 0.0f : bits_f32((uint32_t)biased << 23);
+            for (int i = 0; i < 32; ++i) {
+                float d = v[i] / scale;
+                if (d != d) { q[i] = 0xff; continue; }
+                if (d > 448.0f) d = 448.0f;
+                if (d < -448.0f) d = -448.0f;
+                q[i] = f32_to_e4m3fn(d);
+            }
+        }
+    }
+    return 0;
+}
+
+int mxfp8_oracle_dequantize(const uint8_t* q, const uint8_t* sf, int64_t rows, int64_t cols, int out_dtype, void* out) {
+    if (cols % 32 != 0) return 1;
+    const int64_t nblk = cols / 32;
+    const int64_t sf_cols = round_up(nblk, 4);
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t c = 0; c < cols; ++c) {
+            const uint8_t e = sf[swizzled_sf_offset(r, c / 32, sf_cols)];
+            const float scale = e == 0 ? 0.0f : bits_f32((uint32_t)e << 23);
+            store_from_f32(out, out_dtype, r * cols + c, e4m3fn_to_f32(q[r * cols + c]) * scale);
+        }
+    return 0;
+}
+
 int nvfp4_oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -54,6 +54,10 @@ def lib() -> ctypes.CDLL:
         L.nvfp4_oracle_dynamic_scale.restype = f32
         L.nvfp4_oracle_sf_offset.argtypes = [i64, i64, i64]
         L.nvfp4_oracle_sf_offset.restype = i64
+        L.mxfp8_oracle_quantize.argtypes = [vp, i32, i64, i64, i32, vp, vp]
+        L.mxfp8_oracle_quantize.restype = i32
+        L.mxfp8_oracle_dequantize.argtypes = [vp, vp, i64, i64, i32, vp]
+        L.mxfp8_oracle_dequantize.restype = i32
         L.nvfp4_oracle_num_threads.argtypes = []
         L.nvfp4_oracle_num_threads.restype = i32
         _lib = L
@@ -175,3 +179,40 @@ def rel_rms(y: np.ndarray, y_ref: np.ndarray) -> float:
     y_ref = y_ref.astype(np.float64)
     den = np.sqrt(np.mean(y_ref * y_ref))
     return float(np.sqrt(np.mean((y - y_ref) ** 2)) / (den if den > 0 else 1.0))
+
+
+# ---- MXFP8 (comfy_kitchen/backends/eager/quantization.py:260-405) --------------------------------------------
+
+def quantize_mxfp8(x: np.ndarray, dtype: int, pad_32x: bool = False) -> tuple[np.ndarray, np.ndarray]:
+    """x [rows, cols] -> (e4m3 bytes uint8 [R, C], e8m0 block scales uint8 [roundup(R,128), roundup(C/32,4)] tiled)."""
+    x = _check_input(x, dtype)
+    rows, cols = x.shape
+    prow, pcol = (roundup(rows, 32), roundup(cols, 32)) if pad_32x else (rows, cols)
+    if pcol % 32:
+        raise ValueError("cols must be a multiple of 32 without pad_32x")
+    q = np.empty((prow, pcol), np.uint8)
+    sf = np.empty((roundup(prow, 128), roundup(pcol // 32, 4)), np.uint8)
+    rc = lib().mxfp8_oracle_quantize(_ptr(x), dtype, rows, cols, int(pad_32x), _ptr(q), _ptr(sf))
+    assert rc == 0
+    return q, sf
+
+
+def dequantize_mxfp8(q: np.ndarray, sf: np.ndarray, out_dtype: int = BF16) -> np.ndarray:
+    q, sf = np.ascontiguousarray(q, np.uint8), np.ascontiguousarray(sf, np.uint8)
+    rows, cols = q.shape
+    out = np.empty((rows, cols), np.float32 if out_dtype == F32 else np.uint16)
+    rc = lib().mxfp8_oracle_dequantize(_ptr(q), _ptr(sf), rows, cols, out_dtype, _ptr(out))
+    assert rc == 0
+    return out
+
+
+def scaled_mm_mxfp8(a: np.ndarray, b: np.ndarray, block_scale_a: np.ndarray, block_scale_b: np.ndarray,
+                    bias: np.ndarray | None = None, bias_dtype: int = BF16, out_dtype: int = BF16) -> np.ndarray:
+    """out_dtype( dequant(a) @ dequant(b)^T + bias ) with fp32 accumulation: the check the reference applies to
+    scaled_mm_mxfp8 (dequantize -> linear), like scaled_mm_nvfp4 above."""
+    af = dequantize_mxfp8(a, block_scale_a, F32)
+    bf = dequantize_mxfp8(b, block_scale_b, F32)
+    y = af @ bf.T
+    if bias is not None:
+        y = y + (bias.astype(np.float32) if bias_dtype == F32 else widen(bias, bias_dtype))[None, :]
+    return y if out_dtype == F32 else narrow(np.ascontiguousarray(y, np.float32), out_dtype)

@@ -101,7 +101,8 @@ def test_registers_with_reference_registry(ckb):
         try:
             info = ck.list_backends()["sm100"]
             assert info["available"] and not info["disabled"]
-            assert info["capabilities"] == ["dequantize_nvfp4", "quantize_nvfp4", "scaled_mm_nvfp4"]
+            assert info["capabilities"] == ["dequantize_mxfp8", "dequantize_nvfp4", "quantize_mxfp8", "quantize_nvfp4",
+                                            "scaled_mm_mxfp8", "scaled_mm_nvfp4"]
             assert registry._priority[0] == "sm100"
             assert registry.get_implementation("quantize_nvfp4", backend="sm100") is mod.quantize_nvfp4
             # CPU tensors: our constraints reject them and the registry falls through to eager

@@ -23,6 +23,7 @@ def test_linear_forward_matches_oracle(shape, static_input_scale, oracle):
     lin = ckb.NVFP4Linear.from_float(w, b, input_scale=inp)
     y = lin(x)
     assert tuple(y.shape) == (2, M, N) and y.dtype == torch.bfloat16
+    assert torch.equal(y, lin.forward_unfused(x)), "the one-call linear differs from the three operators"
 
     x2 = x.reshape(-1, K).cpu()
     ts_w = oracle.dynamic_scale(to_bits(w), 2)
@@ -53,3 +54,16 @@ def test_linear_state_dict_round_trip():
     other.load_state_dict(sd)
     x = seeded_randn((32, 256), seed=6).cuda()
     assert torch.equal(lin(x), other(x))
+
+
+def test_linear_small_m_and_fp16(oracle):
+    """M = 1 (split-K path with the workspace's tail as scratch) and fp16 activations through the one-call entry."""
+    import comfy_kitchen_b200 as ckb
+    w = seeded_randn((512, 1024), seed=7, std=0.02).cuda()
+    lin = ckb.NVFP4Linear.from_float(w, None)
+    for m, dtype in ((1, torch.bfloat16), (5, torch.float16), (130, torch.bfloat16)):
+        x = seeded_randn((m, 1024), seed=8 + m, dtype=dtype).cuda()
+        y = lin(x)
+        assert y.dtype == dtype and tuple(y.shape) == (m, 512)
+        assert torch.equal(y, lin.forward_unfused(x))
+    assert ckb.read_device_status() == 0
