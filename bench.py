@@ -447,6 +447,47 @@ def run_ours(args, wl):
             del ww, wq, wsf
         torch.cuda.empty_cache()
 
+    # ---- the MXFP8 sibling path on the same workload (single-GPU runs): quantizer GB/s (3.03125 algorithmic bytes per
+    # element: 2 in, 1 out, 1/32 scale) and GEMM TFLOP/s per linear, with cuBLASLt's MXFP8 kernel beside it ----
+    mxfp8 = None
+    if not distributed and not args.no_sweep:
+        mx_lin, mq_ms, mg_ms, mc_ms, m_fl, m_bytes = [], 0.0, 0.0, 0.0, 0.0, 0.0
+        for i, (name, k, n) in enumerate(wl["linears"]):
+            wq8, wsf8 = ckb.quantize_mxfp8(ws_cpu[i].to(dev), pad_32x=True)
+            xq8, xsf8 = ckb.quantize_mxfp8(xs[i], pad_32x=True)
+            rq8, _ = graphed(lambda i=i: ckb.quantize_mxfp8(xs[i], pad_32x=True))
+            rg8, _ = graphed(lambda xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8: ckb.scaled_mm_mxfp8(xq8, wq8, xsf8, wsf8))
+            tq8 = timed(rq8, args.steps) / args.steps
+            tg8 = timed(rg8, args.steps) / args.steps
+            entry = {"linear": name, "quantize_us": tq8 * 1e3, "quantize_gbs": M * k * 3.03125 / (tq8 * 1e-3) / 1e9,
+                     "gemm_us": tg8 * 1e3, "gemm_tflops": 2.0 * M * n * k / (tg8 * 1e-3) / 1e12}
+            try:
+                from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+
+                def lt(xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8):
+                    return scaled_mm(xq8, wq8.t(), scale_a=xsf8.view(-1), scale_b=wsf8.view(-1),
+                                     scale_recipe_a=ScalingType.BlockWise1x32, scale_recipe_b=ScalingType.BlockWise1x32,
+                                     swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4,
+                                     output_dtype=torch.bfloat16)
+                rc8, _ = graphed(lt)
+                tc8 = timed(rc8, args.steps) / args.steps
+                entry["cublaslt_gemm_tflops"] = 2.0 * M * n * k / (tc8 * 1e-3) / 1e12
+                mc_ms += tc8
+            except Exception as ex:   # depends on the torch / cuBLASLt build
+                entry["cublaslt_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
+            mx_lin.append(entry)
+            mq_ms += tq8
+            mg_ms += tg8
+            m_fl += 2.0 * M * n * k
+            m_bytes += M * k * 3.03125
+            del wq8, wsf8, xq8, xsf8
+            graphs.clear()
+        mxfp8 = {"gemm_tflops": m_fl / (mg_ms * 1e-3) / 1e12, "quantize_gbs": m_bytes / (mq_ms * 1e-3) / 1e9,
+                 "cublaslt_gemm_tflops": (m_fl / (mc_ms * 1e-3) / 1e12) if mc_ms > 0 else None,
+                 "nominal_dense_fp8_tflops": 4500.0, "per_linear": mx_lin,
+                 "kernel": "gemm_nvfp4_kernel<BN, FMT = 1> (1-CTA tiles, tcgen05 kind::mxf8f6f4.block_scale)"}
+        torch.cuda.empty_cache()
+
     # ---- cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend ----
     try:
         from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
@@ -537,7 +578,7 @@ def run_ours(args, wl):
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
-            "quantize_sweep": sweep, "small_m_sweep": small_m,
+            "quantize_sweep": sweep, "small_m_sweep": small_m, "mxfp8": mxfp8,
         }
         if fused:
             # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate

@@ -686,7 +686,18 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
         : "memory");
 }
 
-template <int KB, bool DBG>
+__device__ __forceinline__ void tc_mma_pair_mx(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+constexpr uint32_t kIdesc2Mx = ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24);
+
+// FMT as in gemm_nvfp4_kernel: 0 = NVFP4, 1 = MXFP8 (one scale chunk per stage and band instead of KB / 32).
+template <int KB, bool DBG, int FMT = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -738,7 +749,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     grid_dependency_wait();   // barriers and tensor memory are set up while the previous kernel drains
 
     const int total_tiles = g.m_tiles * g.n_tiles;   // 256 x 256 tiles
-    const int k_stages = (g.sf_cbg + kChunks - 1) / kChunks;   // stages per tile
+    constexpr bool MX = (FMT == 1);
+    constexpr int kSfChunks = MX ? 1 : kChunks;                       // scale chunks per stage and 128-row band
+    constexpr uint32_t kTxBytes = kA2 + kB2 + 3 * kSfChunks * SF_CHUNK_BYTES;   // per CTA and stage
+    const int k_stages = (g.sf_cbg + kSfChunks - 1) / kSfChunks;   // stages per tile
     auto now = [] { return DBG ? clock64() : 0ll; };
 
     if (warp == 0) {
@@ -765,12 +779,12 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const uint32_t st = smem_u32(smem) + stage * kStageBytes2;
                 const uint32_t bar = full0 + stage * 8;
                 if (elect_one()) {
-                    mbar_expect_tx_cluster(bar, kStageBytes2);   // every box is transferred in full (zero fill past the ends)
+                    mbar_expect_tx_cluster(bar, kTxBytes);   // every box is transferred in full (zero fill past the ends)
                     tma_load_2d_pair(st, &tmap_a, kb * KB, a_row, bar);
                     tma_load_2d_pair(st + kA2, &tmap_b, kb * KB, b_row, bar);
-                    tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * kChunks, bar);
-                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * kChunks, bar);
-                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * kChunks, bar);
+                    tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * kSfChunks, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * kSfChunks, bar);
+                    tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * kSfChunks, bar);
                 }
                 __syncwarp();
                 if (++stage == kStages2) { stage = 0; phase ^= 1; }
@@ -816,7 +830,22 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 // scale factors of 64-element step j of the tile go to region (j/2) % 2: two alternating regions,
                 // each holding two steps
                 const int region0 = (kChunks == 2) ? (kb & 1) : 0;
-                if (elect_one()) {
+                if (MX) {
+                    if (elect_one()) {
+                        // one chunk per band and stage; its four bytes per row serve the stage's four instructions
+                        const uint32_t sfa_t = sf_t0 + (uint32_t)(kb & 1) * kSfRegion2, sfb_t = sfa_t + 8;
+                        tc_cp_sf_pair(sfa_t, desc64(sfa_lo, kSfDescHi));
+                        tc_cp_sf_pair(sfb_t, desc64(sfb_lo, kSfDescHi));
+                        tc_cp_sf_pair(sfb_t + 4, desc64(sfb_lo + kSfa2 / 16, kSfDescHi));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_mma_pair_mx(d_tmem, desc64(a_lo + 2 * j, P::kDescHi), desc64(b_lo + 2 * j, P::kDescHi),
+                                           kIdesc2Mx | ((uint32_t)j << 29) | ((uint32_t)j << 4), sfa_t, sfb_t,
+                                           (j != 0 || kb != 0) ? 1u : 0u);
+                        tc_commit_pair(smem_u32(&empty_bar[0]) + stage * 8);
+                        tc_commit_pair(empty_peer + stage * 8);
+                    }
+                } else if (elect_one()) {
 #pragma unroll
                     for (int j = 0; j < kChunks; ++j) {
                         if (j < nchunk) {
@@ -1151,11 +1180,13 @@ int max_active_pairs(int* out) {
     return CK_B200_OK;
 }
 
-template <int KB>
+template <int KB, int FMT = 0>
 int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream) {
     using P = PairCfg<KB>;
     constexpr int kSmemBytes2 = P::kSmemBytes;
-    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true> : gemm_nvfp4_pair_kernel<KB, false>;
+    constexpr int kSfChunks = FMT == 1 ? 1 : P::kChunks;
+    const int64_t row_bytes = FMT == 1 ? K : K / 2;
+    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true, FMT> : gemm_nvfp4_pair_kernel<KB, false, FMT>;
     int pairs = 0;
     if (int rc = max_active_pairs<KB>(&pairs)) return rc;
     cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
@@ -1163,10 +1194,10 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
                     cudaGetErrorString(attr_err));
     CUtensorMap ma, mb, msa, msb, mo;
-    if (int rc = make_operand_map(&ma, a, g.M, K / 2, BM, KB)) return rc;
-    if (int rc = make_operand_map(&mb, b, g.N, K / 2, 128, KB)) return rc;
-    if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg, P::kChunks)) return rc;
-    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, P::kChunks)) return rc;
+    if (int rc = make_operand_map(&ma, a, g.M, row_bytes, BM, KB)) return rc;
+    if (int rc = make_operand_map(&mb, b, g.N, row_bytes, 128, KB)) return rc;
+    if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg, kSfChunks)) return rc;
+    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, kSfChunks)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
         if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
@@ -1175,7 +1206,7 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     }
     g.m_tiles = (int)ceil_div64(g.M, 256);
     g.n_tiles = (int)ceil_div64(g.N, 256);
-    const int64_t row_block_bytes = 256ll * (K / 2);
+    const int64_t row_block_bytes = 256ll * row_bytes;
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 4) group = 4;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
@@ -1473,7 +1504,11 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
     g.debug = g_gemm_debug.load();
     cudaStream_t s = (cudaStream_t)stream;
     float* scratch = (float*)workspace_dev;
-    if (N > 128 && M > 128) return launch_gemm<256, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    // the same choice of tiles as the NVFP4 entry point; variants 1 and 2 force the 1-CTA kernels
+    int variant = g_gemm_variant.load();
+    if (variant == 0 || variant > 3) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
+    if (variant == 3 && M > 128) return launch_gemm_pair<128, 1>(a_dev, b_dev, g, K, s);
+    if (variant == 2 && M > 128) return launch_gemm<256, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
     return launch_gemm<128, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
 }
 

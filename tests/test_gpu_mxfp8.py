@@ -84,13 +84,20 @@ def test_bad_arguments(ckb):
         ckb.quantize_mxfp8(torch.zeros((32, 64), dtype=torch.bfloat16))
 
 
+@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "bn128", "bn256", "pair256"])
+def gemm_variant(request, ckb):
+    prev = ckb.set_tuning(1, request.param)
+    yield request.param
+    ckb.set_tuning(1, prev)
+
+
 GEMM_SHAPES = [(32, 128, 64), (96, 160, 256), (128, 256, 128), (256, 512, 1024), (300, 384, 4096), (1, 1024, 4096),
                (64, 4096, 10240), (1024, 3072, 3072), (520, 1032, 96)]
 
 
 @pytest.mark.parametrize("shape", GEMM_SHAPES, ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_gemm_vs_oracle(shape, with_bias, ckb, oracle):
+def test_gemm_vs_oracle(shape, with_bias, ckb, oracle, gemm_variant):
     M, N, K = shape
     x = seeded_randn((M, K), seed=21).cuda()
     w = seeded_randn((N, K), seed=22, std=0.05).cuda()
@@ -109,7 +116,7 @@ def test_gemm_vs_oracle(shape, with_bias, ckb, oracle):
     assert rel <= REL_RMS_TOL, f"relative RMS error {rel:.3e}"
 
 
-def test_gemm_golden(mx_golden, ckb):
+def test_gemm_golden(mx_golden, ckb, gemm_variant):
     for name in ("gemm_32x128x64", "gemm_96x160x256_bias"):
         qa = torch.from_numpy(mx_golden[f"{name}/qa"]).cuda().view(torch.float8_e4m3fn)
         qb = torch.from_numpy(mx_golden[f"{name}/qb"]).cuda().view(torch.float8_e4m3fn)
