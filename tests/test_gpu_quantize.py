@@ -90,7 +90,10 @@ def test_quantize_vs_oracle(shape, dtype, ckb, oracle, variant):
                               y_ref.view(np.uint32) if out_dt == torch.float32 else y_ref)
 
 
-@pytest.mark.parametrize("shape", [(33, 65), (1, 16), (17, 1000), (129, 130), (5, 7), (200, 24)],
+# the last four: whole 128-column pairs, so the bounds-free walk runs, with input rows that end inside the bottom
+# band (zero rows still inside the padded output) and with both nibble orders
+@pytest.mark.parametrize("shape", [(33, 65), (1, 16), (17, 1000), (129, 130), (5, 7), (200, 24), (200, 256), (1000, 512),
+                                   (4600, 3072), (256, 1024)],
                          ids=lambda s: f"{s[0]}x{s[1]}")
 @pytest.mark.parametrize("hi_first", [True, False])
 def test_quantize_padded_vs_oracle(shape, hi_first, ckb, oracle, variant):
