@@ -2,7 +2,12 @@
 //
 //   out[M,N] = out_dtype( alpha * sum_k e2m1(a[m,k]) e4m3(sfa[m,k/16]) e2m1(b[n,k]) e4m3(sfb[n,k/16]) + bias[n] )
 //
-// Structure (one persistent CTA per SM, 6 warps, no cluster, no multicast):
+// Two kernels share this structure.  gemm_nvfp4_pair_kernel (default for M, N > 128): clusters of two CTAs compute
+// 256 x 256 tiles with cta_group::2 instructions, each CTA loading its 128 rows of A and its half of B.
+// gemm_nvfp4_kernel<BN> (everything else, and split-K for M <= 128): one CTA per 128 x BN tile.  Both take a format
+// parameter: NVFP4 (above) or MXFP8 (e4m3 bytes, e8m0 scale per 32 elements, kind::mxf8f6f4).  No TMA multicast anywhere.
+//
+// Structure of gemm_nvfp4_kernel (one persistent CTA per SM, 6 warps):
 //   warp 0   producer: TMA tile loads of packed A/B (128-byte swizzle) and plain bulk copies of the
 //            scale-factor chunks into a ring of shared-memory stages (mbarrier complete_tx).
 //   warp 1   MMA issuer: copies the stage's scale factors shared -> tensor memory (tcgen05.cp), issues

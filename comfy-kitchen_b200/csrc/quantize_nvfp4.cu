@@ -3,7 +3,10 @@
 // Bandwidth-bound kernels.  Arithmetic reproduces the reference eager backend bit for bit
 // (comfy_kitchen/backends/eager/quantization.py:118-222): amax in the input dtype, three IEEE fp32
 // divisions (amax/6, /per_tensor_scale, x/(per_tensor_scale*block_scale)), RNE to e4m3 and e2m1.
-// Compiled without fast-math; every rounding below is explicit (__fdiv_rn, __fmul_rn, fmaf).
+// Compiled without fast-math; every rounding below is explicit (__fdiv_rn, __fmul_rn, fmaf).  The common path
+// obtains the three correctly rounded quotients without a division instruction (a correctly rounded reciprocal
+// and residual corrections in fused arithmetic); anything unusual (infinities, operands outside the range where
+// that is exact, zero scales) takes IEEE divisions, chosen by warp votes.
 //
 // Work decomposition of the quantizer: one warp handles a "unit" of 4 rows x 64 columns.  The 4 rows
 // are r0 + {0,32,64,96} inside one 128-row band and the 64 columns are one group of 4 scale blocks, so
