@@ -395,7 +395,7 @@ def run_ours(args, wl):
         "per_linear": per_linear,
     }
 
-    # ---- bandwidth sweep of the quantizer / dequantizer (BASELINE configuration 3 shapes), single-GPU runs only:
+    # ---- bandwidth sweep of the quantizer / dequantizer (shapes of the M x K bandwidth-sweep configuration), single-GPU runs only:
     # timed() synchronises all ranks, so every rank would have to run it ----
     sweep = None
     if not distributed and not args.no_sweep:
@@ -417,7 +417,7 @@ def run_ours(args, wl):
             graphs.clear()
         torch.cuda.empty_cache()
 
-    # ---- small-M sweep (BASELINE configuration 5: T5-XXL-style feed-forward, d = 4096, ff = 10240), single-GPU runs:
+    # ---- small-M sweep (T5-XXL-style feed-forward shapes, d = 4096, ff = 10240), single-GPU runs:
     # latency of one linear (quantize + GEMM, split-K below 129 rows) per M ----
     small_m = None
     if not distributed and not args.no_sweep:

@@ -5,7 +5,7 @@ Usage (needs the reference checkout; not needed to run the tests):
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /path/to/comfy-kitchen
 
 Outputs ``nvfp4_golden.npz`` (inputs and outputs of small cases, bit patterns as integers) and
-``nvfp4_golden_large.json`` (SHA-256 digests, byte sums and samples of the BASELINE-sized first
+``nvfp4_golden_large.json`` (SHA-256 digests, byte sums and samples of the full-size single-linear
 config, whose inputs are regenerated from a seeded numpy generator by the tests).
 
 Every expected value comes from calling the reference (``comfy_kitchen`` eager backend,
@@ -38,7 +38,8 @@ def sha(a: np.ndarray) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__))))), "reference"), help="checkout of comfy-kitchen (default: next to this repository)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
@@ -199,7 +200,7 @@ def main() -> None:
     out["names"] = np.array(names)
     np.savez_compressed(os.path.join(here, "nvfp4_golden.npz"), **out)
 
-    # -- first BASELINE configuration (256x1024 activations, 1024x1024 weights), inputs from numpy's generator --
+    # -- the single-linear configuration (256x1024 activations, 1024x1024 weights), inputs from numpy's generator --
     rng = np.random.default_rng(0)
     x32 = rng.standard_normal((256, 1024), dtype=np.float32)
     w32 = (rng.standard_normal((1024, 1024), dtype=np.float32) * np.float32(0.02)).astype(np.float32)

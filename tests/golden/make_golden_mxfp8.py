@@ -19,7 +19,8 @@ import numpy as np
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__))))), "reference"), help="checkout of comfy-kitchen (default: next to this repository)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("COMFY_KITCHEN_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 @pytest.fixture(scope="module")

@@ -1,5 +1,5 @@
 """GPU parity of scaled_mm_nvfp4 (through the C ABI) against the CPU oracle (dequantize -> fp32 matmul), the
-reference golden vectors and, at full BASELINE sizes, torch's cuBLASLt NVFP4 matmul on the same operands.
+reference golden vectors and, at the full benchmark sizes, torch's cuBLASLt NVFP4 matmul on the same operands.
 
 Tolerance (floating point): relative RMS error <= 1e-2 against the reference path on identical quantized
 operands; in practice the error is bf16 output rounding (~2e-3)."""
@@ -139,7 +139,7 @@ WAN_T5 = [(32760, 5120, 5120), (32760, 13824, 5120), (512, 10240, 4096), (64, 40
 
 @pytest.mark.parametrize("mnk", FLUX + WAN_T5, ids=lambda s: "x".join(map(str, s)))
 def test_gemm_full_size_vs_cublaslt(mnk, ckb, variant):
-    """BASELINE-sized linears: same quantized operands through torch's cuBLASLt NVFP4 matmul (the kernel behind the
+    """Benchmark-sized linears: same quantized operands through torch's cuBLASLt NVFP4 matmul (the kernel behind the
     reference eager backend) and through ours; plus linearity in alpha, which needs no reference at all."""
     M, N, K = mnk
     x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=K + N, outliers=True)
