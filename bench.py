@@ -556,7 +556,7 @@ def run_ours(args, wl):
         cpu_reference_step(wl, xs_bits, w_q, rows)
         t0 = time.perf_counter()
         reps, cfl = 0, 0.0
-        while reps < 2 or (time.perf_counter() - t0 < 10.0 and reps < 20):
+        while reps < 2 or (time.perf_counter() - t0 < 12.0 and reps < 200):
             cfl += cpu_reference_step(wl, xs_bits, w_q, rows)
             reps += 1
         dt = time.perf_counter() - t0
