@@ -324,7 +324,8 @@ float nvfp4_oracle_dynamic_scale(const void* x, int dtype, int64_t n) {
  * e8m0_to_f32 (comfy_kitchen/float_utils.py:376-382).  One deliberate difference, stated here and checked by
  * the golden vectors: the reference takes ceil(log2(amax/448)) with a float32 log2, which rounds a quotient
  * that lies within ~2.6e-6 above a power of two down onto it (one exponent lower); this restatement takes the
- * exact ceiling.  The reference's own tests allow +-1 on the exponent between its backends
+ * exact ceiling, like the reference's CUDA kernel (comfy_kitchen/backends/cuda/ops/quantize_mxfp8.cu:56-64, e8m0
+ * conversion rounding toward +infinity).  The reference's own tests allow +-1 on the exponent between its backends
  * (tests/test_qdq.py:431-438); on bf16 and fp16 inputs the two agree always (amax/448 cannot come that close).
  */
 
