@@ -73,6 +73,9 @@ struct GemmArgs {
     int splits;           // split-K: every tile is computed by `splits` work items over k_per_split stages each,
     int k_per_split;      //          which leave fp32 partial sums in `partial` for splitk_reduce_kernel
     float* partial;       // [splits, M, N] fp32 scratch (split-K only)
+    int a_box_bytes;      // bytes one TMA load of A delivers per stage in the 1-CTA kernel: the box covers only
+                          // 32 or 64 rows when M is that small (the rows above stay unwritten and feed accumulator
+                          // rows that are never stored)
     int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
     int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
     // fused all-gather (CTA-pair kernel, 16-bit output): `out` is this rank's column block inside its own
@@ -389,7 +392,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const int nchunk = MX ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
                 const uint32_t sf_bytes = nchunk * SF_CHUNK_BYTES;
                 if (elect_one()) {
-                    mbar_expect_tx(bar, C::kABytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
+                    mbar_expect_tx(bar, g.a_box_bytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
                     tma_load_2d(st, &tmap_a, kb * BK_BYTES, tm * BM, bar);
                     tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * BN, bar);
                     bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)chunk0 * SF_CHUNK_BYTES, sf_bytes, bar);
@@ -1248,7 +1251,9 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
                     cudaGetErrorString(attr_err));
     CUtensorMap ma, mb, mo;
-    if (int rc = make_operand_map(&ma, a, g.M, row_bytes, BM)) return rc;
+    const int a_box_rows = g.M <= 32 ? 32 : g.M <= 64 ? 64 : BM;
+    g.a_box_bytes = a_box_rows * BK_BYTES;
+    if (int rc = make_operand_map(&ma, a, g.M, row_bytes, a_box_rows)) return rc;
     if (int rc = make_operand_map(&mb, b, g.N, row_bytes, BN)) return rc;
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
     if (g.tma_store) {
@@ -1348,6 +1353,7 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
     g.ld_out = N;
@@ -1501,6 +1507,7 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
     g.ld_out = N;
