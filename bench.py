@@ -243,8 +243,8 @@ def run_ours(args, wl):
 
     equal_shards = all(n % (8 * world) == 0 for _, _, n in wl["linears"])
     peers = None
-    if fused and not (equal_shards and M % 16 == 0 and all(n // world > 128 for _, _, n in wl["linears"])):
-        fused = False            # the fused kernel wants equal shards wider than 128 columns and M % 16 == 0
+    if fused and not (equal_shards and M > 128 and all(n // world > 128 for _, _, n in wl["linears"])):
+        fused = False            # the fused kernel wants equal shards wider than 128 columns and more than 128 rows
         use_graph = False
     if fused:
         peers = ckb.PeerGroup(dev)

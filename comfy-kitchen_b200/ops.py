@@ -186,11 +186,11 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
 def scaled_mm_nvfp4_all_gather(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tensor,
                                tensor_scale_b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
                                out_ptrs: list[int], rank: int, out_dtype: torch.dtype = torch.bfloat16,
-                               bias: torch.Tensor | None = None) -> None:
+                               bias: torch.Tensor | None = None, rows: int | None = None) -> None:
     """scaled_mm_nvfp4 of this rank's weight shard ``b`` [N_local, K/2], written into columns
     [rank*N_local, (rank+1)*N_local) of every rank's [M, world*N_local] matrix (``out_ptrs``: device addresses by rank,
     peers' matrices as mapped by ``peer_open``).  Returns nothing: the matrices are complete after the next
-    ``peer_barrier`` on every rank."""
+    ``peer_barrier`` on every rank.  ``rows``: number of rows of ``a`` to use (the output matrices have that many)."""
     a, b = _plain(a), _plain(b)
     block_scale_a, block_scale_b = _plain(block_scale_a), _plain(block_scale_b)
     _require_cuda(a, "a")
@@ -201,6 +201,9 @@ def scaled_mm_nvfp4_all_gather(a: torch.Tensor, b: torch.Tensor, tensor_scale_a:
     assert b.shape[1] == k_half and a.is_contiguous() and b.is_contiguous()
     sk = roundup(2 * k_half // 16, 4)
     assert tuple(block_scale_a.shape) == (roundup(m, 128), sk), "Invalid A scale shape"
+    if rows is not None:     # `a` was padded to 16 rows by the quantizer: only the first `rows` are multiplied and stored
+        assert 0 < rows <= m and roundup(rows, 128) == roundup(m, 128)
+        m = rows
     assert tuple(block_scale_b.shape) == (roundup(n_local, 128), sk), "Invalid B scale shape"
     bias_code = 2
     if bias is not None:

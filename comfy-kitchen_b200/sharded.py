@@ -231,10 +231,9 @@ class ShardedNVFP4Linear:
         ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
         pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
         qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
-        if qx.shape[0] != x.shape[0]:
-            raise ValueError("the fused all-gather needs a row count that is a multiple of 16")
         self.ops.scaled_mm_nvfp4_all_gather(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
-                                            self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias)
+                                            self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias,
+                                            rows=x.shape[0])
         return self.out_full
 
     def gather_async(self, y_local: torch.Tensor):

@@ -34,16 +34,15 @@ def test_emulated_ranks_match_unsharded(shape, with_bias):
     pad = M % 16 != 0
     qx, sfx = ckb.quantize_nvfp4(x, tsx, pad_16x=pad)
     qw, sfw = ckb.quantize_nvfp4(w, tsw)
-    Mp = qx.shape[0]
-    want = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
+    want = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)[:M]
     n_local = N // world
-    outs = [torch.full((Mp, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]   # M rows: unpadded
     ptrs = [o.data_ptr() for o in outs]
     for rank in range(world):
         shard = w[rank * n_local:(rank + 1) * n_local].contiguous()
         qs, sfs = ckb.quantize_nvfp4(shard, tsw)
         b = None if bias is None else bias[rank * n_local:(rank + 1) * n_local].contiguous()
-        ops.scaled_mm_nvfp4_all_gather(qx, qs, tsx, tsw, sfx, sfs, ptrs, rank, bias=b)
+        ops.scaled_mm_nvfp4_all_gather(qx, qs, tsx, tsw, sfx, sfs, ptrs, rank, bias=b, rows=M)
     torch.cuda.synchronize()
     assert ckb.read_device_status() == 0
     for r, o in enumerate(outs):
