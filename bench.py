@@ -516,27 +516,57 @@ def run_ours(args, wl):
     h2d = sum(x.numel() * 2 for x in x_host)
     d2h = sum(y.numel() * 2 for y in y_host)
 
+    # Three streams: uploads, the operators (the current stream), downloads.  PCIe carries both directions at once and
+    # the GPU has separate copy engines for them, so linear i's output goes back while linear i+1's activations come
+    # in, also across step boundaries; events order upload -> operators -> download per linear.  Each linear has
+    # its own device input buffer, reused every step once the operators of the previous step have read it.
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    x_dev = [torch.empty_like(x) for x in xs]
+    ev_in = [torch.cuda.Event() for _ in layers]
+    ev_cmp = [torch.cuda.Event() for _ in layers]
+    ev_out = [torch.cuda.Event() for _ in layers]
+    serial = args.e2e_serial
+
     def e2e_step():
-        for xh, yh, lin in zip(x_host, y_host, layers):
-            xd = xh.to(dev, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        for i, (xh, yh, lin) in enumerate(zip(x_host, y_host, layers)):
+            s_in.wait_event(ev_cmp[i])                     # last step's operators are done with x_dev[i]
+            if serial:
+                s_in.wait_stream(s_out)
+            with torch.cuda.stream(s_in):
+                x_dev[i].copy_(xh, non_blocking=True)
+                ev_in[i].record()
+            cur.wait_event(ev_in[i])
             if fused:
+                cur.wait_event(ev_out[i])                  # last step's download has read this rank's matrix
                 peers.barrier()
-                y = lin.fused(xd)
+                y = lin.fused(x_dev[i])
                 peers.barrier()
                 y = y[:, lin.n0:lin.n1]
             else:
-                y = lin.local(xd)
+                y = lin.local(x_dev[i])
                 if distributed:
                     y = lin.gather(y, row_major=False)[rank]
-            yh.copy_(y, non_blocking=True)
+            ev_cmp[i].record()
+            s_out.wait_event(ev_cmp[i])
+            with torch.cuda.stream(s_out):
+                yh.copy_(y, non_blocking=True)
+                ev_out[i].record()
+            y.record_stream(s_out)
+            if serial:
+                cur.wait_stream(s_out)
+        cur.wait_stream(s_out)                             # the closing event of the timed region covers the downloads
 
     for _ in range(2):
         e2e_step()
     ems = timed(e2e_step, args.steps)
     e2e = {"value": fl * args.steps / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
+           "pcie_gbs": {"h2d": h2d / (ems / args.steps * 1e-3) / 1e9, "d2h": d2h / (ems / args.steps * 1e-3) / 1e9},
            "what": "pinned host bf16 activations -> device, quantize_nvfp4 + scaled_mm_nvfp4 through the operator "
-                   "interface, bf16 outputs -> pinned host; per rank"}
+                   "interface, bf16 outputs -> pinned host; per rank; "
+                   + ("one transfer at a time" if serial else
+                      "uploads, operators and downloads on three streams, so the two PCIe directions overlap")}
     if args.gemm_debug and rank == 0:
         # one launch per linear of the kernel build with cycle counters: CTA pair 0 prints (device printf, on stdout
         # before the JSON line) the cycles and nanoseconds its roles took and how long they waited
@@ -611,6 +641,8 @@ def main():
                     help="N > 1: all-gather fused into the GEMM epilogue over peer memory, or a NCCL all-gather after it")
     ap.add_argument("--gemm-debug", action="store_true",
                     help="also launch each linear's GEMM once with in-kernel cycle counters (prints extra lines)")
+    ap.add_argument("--e2e-serial", action="store_true",
+                    help="end-to-end arm: one host<->device transfer at a time instead of overlapping the two directions")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
