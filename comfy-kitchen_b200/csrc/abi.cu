@@ -11,6 +11,7 @@ std::atomic<int> g_quant_variant{2};
 std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
+std::atomic<int> g_linear_fused{1};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -91,6 +92,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_DEPENDENT_LAUNCH: return ckb::g_dependent_launch.exchange(value);
         case CK_B200_TUNE_GEMM_VARIANT: return ckb::g_gemm_variant.exchange(value);
         case CK_B200_TUNE_GEMM_DEBUG: return ckb::g_gemm_debug.exchange(value);
+        case CK_B200_TUNE_LINEAR_FUSED: return ckb::g_linear_fused.exchange(value);
         default: return -1;
     }
 }
@@ -145,13 +147,16 @@ int ck_b200_peer_free(void* ptr) {
 namespace {
 struct LinearPlan {
     int64_t prow;          // activation rows after padding to 16
-    size_t scale_off, q_off, sf_off, end;   // byte offsets inside the workspace
+    size_t scale_off, q_off, sf_off, sync_off, end;   // byte offsets inside the workspace
 };
 LinearPlan plan_linear(int64_t M, int64_t K) {
     LinearPlan p;
     p.prow = ckb::round_up64(M, 16);
     p.scale_off = 0;
-    p.q_off = 256;
+    // the sync area of the fused kernel sits at the same place for every shape, so that nothing but that kernel
+    // ever writes there when linears of different shapes share one workspace
+    p.sync_off = 256;
+    p.q_off = p.sync_off + ckb::fused_sync_bytes();
     p.sf_off = p.q_off + (size_t)ckb::round_up64(p.prow * (K / 2), 256);
     p.end = p.sf_off + (size_t)ckb::round_up64(ckb::round_up64(p.prow, 128) * ckb::round_up64(K / 16, 4), 256);
     return p;
@@ -185,6 +190,11 @@ int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, c
     }
     void* qx = ws + p.q_off;
     void* sfx = ws + p.sf_off;
+    // more than one tile row and column: the GEMM kernel quantizes the activations itself, beside its main loop
+    if (ckb::g_linear_fused.load() && ckb::g_gemm_variant.load() == 0 &&
+        ckb::fused_linear_supported(x_dtype, x_dev, M, N, K, out_dtype))
+        return ckb::fused_linear_launch(x_dev, x_dtype, M, K, ts_x, qx, sfx, ws + p.sync_off, w_q_dev, w_sf_dev,
+                                        w_scale_dev, N, bias_dev_or_null, bias_dtype, out_dev, out_dtype, stream);
     if (int rc = ck_b200_quantize_nvfp4(x_dev, x_dtype, ts_x, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1, stream))
         return rc;
     // what is left of the workspace serves the split-K reduction of small-M problems

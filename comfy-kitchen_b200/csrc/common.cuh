@@ -28,6 +28,16 @@ extern std::atomic<int> g_dependent_launch;
 // Checks that the current device is compute capability 10.x (cached per device ordinal).
 int check_device(int* sm_count_out);
 
+// The CTA-pair GEMM with the activation quantizer inside (gemm_nvfp4_sm100.cu): whether a linear can take that
+// path, the bytes of its sync area, and the launch.  qx / sfx receive the quantized activations (rows padded to 16).
+extern std::atomic<int> g_linear_fused;
+bool fused_linear_supported(int x_dtype, const void* x_dev, int64_t M, int64_t N, int64_t K, int out_dtype);
+size_t fused_sync_bytes();
+int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* ts_x_dev, void* qx_dev,
+                        void* sfx_dev, void* sync_dev, const void* w_q_dev, const void* w_sf_dev,
+                        const float* w_scale_dev, int64_t N, const void* bias_dev_or_null, int bias_dtype, void* out_dev,
+                        int out_dtype, void* stream);
+
 #define CKB_CUDA_OK(expr)                                                                              \
     do {                                                                                               \
         cudaError_t e__ = (expr);                                                                      \

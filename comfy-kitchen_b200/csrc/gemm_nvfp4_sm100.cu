@@ -37,6 +37,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "quantize_nvfp4_device.cuh"
 
 namespace ckb {
 namespace {
@@ -53,7 +54,7 @@ constexpr int STAGING_BYTES_PER_WARP = 32 * EPI_COLS * 2;   // 32 rows x 32 sixt
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // about 1.5 s
 
 enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5,
-                WAIT_PEER_BARRIER = 6 };
+                WAIT_PEER_BARRIER = 6, WAIT_QUANT_BAND = 7 };
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -704,12 +705,65 @@ __device__ __forceinline__ void tc_mma_pair_mx(uint32_t d_tmem, uint64_t adesc, 
 }
 constexpr uint32_t kIdesc2Mx = ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24);
 
+// ---- activation quantizer inside the pair kernel --------------------------------------------------------
+//
+// gemm_nvfp4_pair_kernel<.., QDT >= 0> carries eight more warps per CTA that quantize the activation matrix (dtype
+// code QDT) into the packed operand and scale tensor the kernel's own TMA loads read: the quantizer, which is bound
+// by HBM, then runs beside the tensor-core main loop instead of in front of it.  Tiles are walked one row block
+// after the other, so the first wave of tiles needs only the first few 128-row bands and the quantizer warps (which
+// take the bands in the same order and never wait for anything) stay ahead of the loads from then on.
+//
+// Progress is published per band in 64-bit words {epoch : count} in a small sync area of the caller's workspace.  A
+// word counts only while its upper half equals the current epoch, which the last CTA to leave the kernel advances,
+// so the words need no initialisation and no clean-up, and replays of a captured launch work like fresh ones.
+// A producer warp polls its band's word (bounded, like every wait here) before the first load of a tile, then
+// orders its TMA loads after what it has seen with a proxy fence.  Calls that share a workspace must not overlap
+// on the GPU (they would also share the quantized operand).
+constexpr int kQuantWarps = 8;
+struct FusedQuantSync {
+    uint32_t epoch;
+    uint32_t pad;
+    unsigned long long exits;       // CTAs that have left the kernel
+    unsigned long long bands_done;  // bands completely quantized
+    unsigned long long band[1];     // [bands] warps done with their segment of the band
+};
+struct FusedQuant {
+    QuantArgs q;
+    FusedQuantSync* sync;
+    int bands;
+};
+
+// Adds one to the count of *w for `epoch` (a word of another epoch counts as zero); returns the new count.
+__device__ __forceinline__ uint32_t epoch_arrive(unsigned long long* w, uint32_t epoch) {
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(w);
+    for (;;) {
+        const uint32_t count = ((uint32_t)(old >> 32) == epoch) ? (uint32_t)old : 0u;
+        const unsigned long long want = ((unsigned long long)epoch << 32) | (unsigned long long)(count + 1u);
+        const unsigned long long seen = atomicCAS(w, old, want);
+        if (seen == old) return count + 1u;
+        old = seen;
+    }
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // FMT as in gemm_nvfp4_kernel: 0 = NVFP4, 1 = MXFP8 (one scale chunk per stage and band instead of KB / 32).
-template <int KB, bool DBG, int FMT = 0>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+// QDT: -1 = operands come quantized; otherwise the dtype code of the activations that eight extra warps quantize.
+template <int KB, bool DBG, int FMT = 0, int QDT = -1>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                       const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
+                       const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g, const FusedQuant fq) {
+    constexpr bool QF = QDT >= 0;
     using P = PairCfg<KB>;
     constexpr int kStages2 = P::kStages, kStageBytes2 = P::kStageBytes, kA2 = P::kA, kB2 = P::kB, kSfa2 = P::kSfa;
     constexpr int kChunks = P::kChunks;
@@ -771,6 +825,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         long long waited = 0;
         const long long t_begin = now();
         const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);   // CTA 0's barriers
+        bool q_all_ready = false;
+        long long q_waited = 0;
+        unsigned long long q_band_target = 0, q_all_target = 0;
+        if (QF) {
+            const unsigned long long e = (unsigned long long)ld_relaxed_u32(&fq.sync->epoch) << 32;
+            q_band_target = e | (unsigned long long)(32 * fq.q.segments);
+            q_all_target = e | (unsigned long long)fq.bands;
+        }
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
             int tm, tn;
             tile_coords(g, tile, tm, tn);
@@ -778,6 +840,34 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int b_row = tn * 256 + (int)rank * 128;                // this CTA's half of the B tile
             const int sfa_chunk0 = (tm * 2 + (int)rank) * g.sf_cbg;
             const int sfb_chunk0 = tn * 2 * g.sf_cbg;
+            if (QF && !q_all_ready) {
+                // this CTA's A rows and their scales are one band of the activation matrix: wait until the
+                // quantizer warps (of any CTA) have finished it
+                const int band = tm * 2 + (int)rank;
+                const long long t0 = now();
+                if (lane == 0) {
+                    if (ld_acquire_u64(&fq.sync->bands_done) == q_all_target) {
+                        q_all_ready = true;
+                    } else if (band < fq.bands) {
+                        const long long start = clock64();
+                        while (ld_acquire_u64(&fq.sync->band[band]) != q_band_target) {
+                            if (*abort_flag) { ok = false; break; }
+                            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                                *abort_flag = 1;
+                                atomicCAS(&g_device_status, 0, (int)WAIT_QUANT_BAND);
+                                ok = false;
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                    fence_proxy_async_all();   // the loads below read what the quantizer warps wrote with plain stores
+                }
+                q_all_ready = __shfl_sync(0xffffffffu, (int)q_all_ready, 0) != 0;
+                ok = __all_sync(0xffffffffu, ok);
+                q_waited += now() - t0;
+                if (!ok) break;
+            }
             for (int kb = 0; kb < k_stages; ++kb) {
                 const long long t0 = now();
                 ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
@@ -799,8 +889,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             }
         }
         if (DBG && pair == 0 && lane == 0)
-            printf("[gemm pair cta%u] producer: total %lld cycles, waiting for free stages %lld\n", rank, now() - t_begin,
-                   waited);
+            printf("[gemm pair cta%u] producer: total %lld cycles, waiting for free stages %lld, for quantized bands %lld\n",
+                   rank, now() - t_begin, waited, q_waited);
     } else if (warp == 1 && rank == 0) {
         // ---------------- MMA issuer (CTA 0 of the pair) ----------------
         int stage = 0, acc = 0, local_tile = 0;
@@ -893,6 +983,30 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (DBG && pair == 0 && lane == 0)
             printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n",
                    now() - t_begin, wait_acc, wait_full);
+    } else if (QF && warp >= NUM_THREADS / 32) {
+        // ---------------- activation quantizer (eight warps of both CTAs) ----------------
+        if constexpr (QF) {
+            const long long t_begin = now();
+            const uint32_t epoch = ld_relaxed_u32(&fq.sync->epoch);
+            const float ts = __ldg(fq.q.pts);
+            const int per_band = 32 * fq.q.segments;
+            const int items = fq.bands * per_band;
+            const int stride = (int)gridDim.x * kQuantWarps;
+            for (int item = (int)blockIdx.x * kQuantWarps + (warp - NUM_THREADS / 32); item < items; item += stride) {
+                const int band = item / per_band;
+                const int rem = item - band * per_band;
+                quantize_segment<QDT, true, 2>(fq.q, rem >> 5, band * 32 + (rem & 31), lane, ts);
+                __threadfence();
+                fence_proxy_async_all();
+                __syncwarp();
+                if (lane == 0 && epoch_arrive(&fq.sync->band[band], epoch) == (uint32_t)per_band) {
+                    __threadfence();
+                    epoch_arrive(&fq.sync->bands_done, epoch);
+                }
+            }
+            if (DBG && pair == 0 && threadIdx.x == NUM_THREADS)
+                printf("[gemm pair cta%u] quantizer: total %lld cycles\n", rank, now() - t_begin);
+        }
     } else if (warp >= 2) {
         // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
         const int quad = warp & 3;
@@ -1017,6 +1131,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+    if (QF && threadIdx.x == 0) {
+        // every warp of this CTA is past its last use of the sync words; the last CTA out starts the next epoch
+        const uint32_t epoch = ld_relaxed_u32(&fq.sync->epoch);
+        __threadfence();
+        if (epoch_arrive(&fq.sync->exits, epoch) == gridDim.x) {
+            __threadfence();
+            atomicAdd(&fq.sync->epoch, 1u);
+        }
     }
 }
 
@@ -1157,20 +1280,21 @@ int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks, int box_ch
 }
 
 // Pairs of CTAs that can be resident at once (clusters of 2 need two free SMs of one GPC), cached per device.
-template <int KB>
+template <int KB, int QDT = -1>
 int max_active_pairs(int* out) {
     constexpr int kSmemBytes2 = PairCfg<KB>::kSmemBytes;
+    constexpr int kThreads = QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS;
     static std::mutex mu;
     static int cache[64] = {0};
     int dev = 0;
     CKB_CUDA_OK(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == 0) {
-        auto kernel = gemm_nvfp4_pair_kernel<KB, false>;
+        auto kernel = gemm_nvfp4_pair_kernel<KB, false, 0, QDT>;
         CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * 148);
-        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = kSmemBytes2;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -1188,15 +1312,23 @@ int max_active_pairs(int* out) {
     return CK_B200_OK;
 }
 
-template <int KB, int FMT = 0>
-int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream) {
+// QDT >= 0: the kernel also quantizes the activations described by *fused (dtype code QDT) into `a` and g.sfa.
+template <int KB, int FMT = 0, int QDT = -1>
+int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream,
+                     const FusedQuant* fused = nullptr) {
     using P = PairCfg<KB>;
     constexpr int kSmemBytes2 = P::kSmemBytes;
     constexpr int kSfChunks = FMT == 1 ? 1 : P::kChunks;
+    constexpr int kThreads = QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS;
     const int64_t row_bytes = FMT == 1 ? K : K / 2;
-    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true, FMT> : gemm_nvfp4_pair_kernel<KB, false, FMT>;
+    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true, FMT, QDT> : gemm_nvfp4_pair_kernel<KB, false, FMT, QDT>;
     int pairs = 0;
-    if (int rc = max_active_pairs<KB>(&pairs)) return rc;
+    if (int rc = max_active_pairs<KB, QDT>(&pairs)) return rc;
+    FusedQuant fq{};
+    if (QDT >= 0) {
+        if (!fused) return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused quantizer: missing description");
+        fq = *fused;
+    }
     cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
     if (attr_err != cudaSuccess)
         return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
@@ -1218,12 +1350,14 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 4) group = 4;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
+    // with the quantizer inside, tiles go row block by row block: the first wave then waits for a few bands only
+    if (QDT >= 0) g.raster_group = 1;
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
-    const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), kSmemBytes2, stream, ma, mb, msa, msb, mo, g);
+    const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(kThreads), kSmemBytes2, stream, ma, mb, msa, msb, mo, g, fq);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
     return CK_B200_OK;
@@ -1312,7 +1446,7 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
                    const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
                    const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N,
                    int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream,
-                   const GatherSpec* gather = nullptr) {
+                   const GatherSpec* gather = nullptr, const FusedQuant* fused = nullptr, int fused_dtype = -1) {
     int sms = 0;
     if (int rc = check_device(&sms)) return rc;
     if (!a_dev || !sfa_dev || !b_dev || !sfb_dev || !out_dev)
@@ -1377,6 +1511,15 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
         for (int p = 0; p < gather->n_peers; ++p) g.peer_out[p] = gather->peers[p];
         return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     }
+    if (fused) {
+        if (M <= 128 || N <= 128)
+            return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused quantizer: needs M > 128 and N > 128");
+        if (fused_dtype == CK_B200_DTYPE_BF16)
+            return launch_gemm_pair<128, 0, CK_B200_DTYPE_BF16>(a_dev, b_dev, g, K, s, fused);
+        if (fused_dtype == CK_B200_DTYPE_F16)
+            return launch_gemm_pair<128, 0, CK_B200_DTYPE_F16>(a_dev, b_dev, g, K, s, fused);
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused quantizer: activations must be bf16 or fp16");
+    }
     if (variant == 4 && M > 128) return launch_gemm_pair<64>(a_dev, b_dev, g, K, s);
     if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
@@ -1394,6 +1537,51 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
                           bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, workspace_dev, workspace_bytes, stream);
 }
 
+
+// ---- GEMM that quantizes its own activations -------------------------------------------------------------
+
+namespace ckb {
+constexpr size_t kFusedSyncBytes = 32768;
+constexpr int64_t kFusedMaxBands = (int64_t)(kFusedSyncBytes - sizeof(FusedQuantSync)) / 8;
+size_t fused_sync_bytes() { return kFusedSyncBytes; }
+
+bool fused_linear_supported(int x_dtype, const void* x_dev, int64_t M, int64_t N, int64_t K, int out_dtype) {
+    return (x_dtype == CK_B200_DTYPE_BF16 || x_dtype == CK_B200_DTYPE_F16) && M > 128 && N > 128 && K % 32 == 0 &&
+           K >= 384 && (((uintptr_t)x_dev & 15) == 0) && ceil_div64(M, 128) <= kFusedMaxBands && K < 0x3fffff00ll &&
+           out_dtype >= 0;
+}
+
+int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* ts_x_dev, void* qx_dev,
+                        void* sfx_dev, void* sync_dev, const void* w_q_dev, const void* w_sf_dev,
+                        const float* w_scale_dev, int64_t N, const void* bias_dev_or_null, int bias_dtype, void* out_dev,
+                        int out_dtype, void* stream) {
+    if (!x_dev || !ts_x_dev || !qx_dev || !sfx_dev || !sync_dev || ((uintptr_t)sync_dev & 7))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused linear: null or misaligned pointer");
+    FusedQuant fq;
+    QuantArgs& a = fq.q;
+    a.x = x_dev;
+    a.pts = ts_x_dev;
+    a.q = (uint8_t*)qx_dev;
+    a.sf = (uint8_t*)sfx_dev;
+    a.rows = (int)M;
+    a.cols = (int)K;
+    a.prow = (int)round_up64(M, 16);
+    a.pcol = (int)K;   // K % 32 == 0
+    a.row_groups = (int)(round_up64(a.prow, 128) / 4);
+    a.sf_cbg = (int)(round_up64(K / 16, 4) / 4);
+    // about eight segments per row, each an even number of units and at least one prefetch ring long: short
+    // enough that the bands finish one after the other, in the order in which the tiles need them
+    int su = (int)round_up64(ceil_div64(a.sf_cbg, 8), 2);
+    if (su < kRing) su = kRing;
+    a.seg_units = su;
+    a.segments = (int)ceil_div64(a.sf_cbg, su);
+    a.hi_first = 1;
+    fq.sync = (FusedQuantSync*)sync_dev;
+    fq.bands = a.row_groups / 32;
+    return scaled_mm_impl(qx_dev, sfx_dev, w_q_dev, w_sf_dev, ts_x_dev, w_scale_dev, nullptr, bias_dev_or_null,
+                          bias_dtype, out_dev, out_dtype, M, N, K, nullptr, 0, stream, nullptr, &fq, x_dtype);
+}
+}  // namespace ckb
 
 // ---- GEMM fused with the all-gather of its column blocks ----------------------------------------------
 

@@ -374,6 +374,7 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
     with torch.cuda.device(x.device):
         if ws is None or ws.numel() < need:
             ws = torch.empty(max(need, 64 << 20), dtype=torch.uint8, device=x.device)
+            ws[: 1 << 16].zero_()      # the fused kernel's progress words start from zero
             _LINEAR_WS[idx] = ws
         w_ts = _scale_on(x.device, weight_scale)
         in_ts = None if input_scale is None else _scale_on(x.device, input_scale)

@@ -67,3 +67,60 @@ def test_linear_small_m_and_fp16(oracle):
         assert y.dtype == dtype and tuple(y.shape) == (m, 512)
         assert torch.equal(y, lin.forward_unfused(x))
     assert ckb.read_device_status() == 0
+
+
+FUSED_SHAPES = [(256, 256, 512), (300, 384, 1024), (1000, 768, 3072), (4608, 3072, 3072), (520, 1024, 416),
+                (2049, 512, 12288)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_linear_quantizer_inside_the_gemm(dtype):
+    """M > 128 and N > 128: one kernel quantizes the activations beside the tensor-core main loop.  Results must be
+    bit-identical to the separate operators, over a sequence of shapes that share the workspace (rows that are not
+    multiples of 16 or 128, K that is not a multiple of 128), with a dynamic and with a static activation scale."""
+    import comfy_kitchen_b200 as ckb
+    for i, (M, N, K) in enumerate(FUSED_SHAPES * 2):
+        w = seeded_randn((N, K), seed=20 + i, std=0.02).cuda()
+        b = seeded_randn((1, N), seed=40 + i, std=0.1, dtype=dtype).reshape(N).cuda()
+        x = seeded_randn((M, K), seed=60 + i, dtype=dtype, outlier_cols=3).cuda()
+        inp = torch.tensor(0.0171, dtype=torch.float32) if i % 2 else None
+        lin = ckb.NVFP4Linear.from_float(w, b, input_scale=inp)
+        want = lin.forward_unfused(x)
+        for _ in range(3):
+            got = lin(x)
+            assert got.dtype == dtype and torch.equal(got, want), f"{M}x{N}x{K}: fused linear differs"
+    assert ckb.read_device_status() == 0
+
+
+def test_linear_quantizer_inside_the_gemm_can_be_switched_off_and_replayed():
+    import comfy_kitchen_b200 as ckb
+    M, N, K = 1024, 1024, 2048
+    w = seeded_randn((N, K), seed=81, std=0.02).cuda()
+    x = seeded_randn((M, K), seed=82).cuda()
+    lin = ckb.NVFP4Linear.from_float(w, None, input_scale=torch.tensor(0.02))
+    want = lin.forward_unfused(x)
+    n0 = ckb.launches()
+    y = lin(x)
+    assert ckb.launches() - n0 == 1, "the fused linear is one kernel when the activation scale is static"
+    assert torch.equal(y, want)
+    old = ckb.set_tuning(4, 0)
+    try:
+        n0 = ckb.launches()
+        assert torch.equal(lin(x), want)
+        assert ckb.launches() - n0 == 2
+    finally:
+        ckb.set_tuning(4, old)
+    # replays of a captured call: the progress words carry over from one replay to the next
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        lin(x)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        y = lin(x)
+    for it in range(4):
+        x.copy_(seeded_randn((M, K), seed=90 + it).cuda())
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, lin.forward_unfused(x))
+    assert ckb.read_device_status() == 0
