@@ -229,6 +229,11 @@ def run_ours(args, wl):
     # but the process then hung while tearing the process group down, so library collectives stay out of graphs
     fused = distributed and args.collective == "fused"
     use_graph = (not distributed or fused) and not args.no_graph
+    # --fused-linear: each linear is one call of the library's whole-linear entry point with the quantizer inside
+    # the GEMM kernel (same bits as quantize_nvfp4 followed by scaled_mm_nvfp4; measured slower, so not the default)
+    one_call = args.fused_linear
+    if one_call:
+        ckb.set_tuning(4, 1)
 
     M = wl["M"]
     pad_m = M % 16 != 0
@@ -251,7 +256,7 @@ def run_ours(args, wl):
         for lin in layers:
             lin.bind(peers, M)
 
-    def step():
+    def step(one_call=one_call):
         # the linears of a step are independent work items: the all-gather of one overlaps the quantizer and GEMM
         # of the next (the collective runs on the process group's stream); all of them are awaited before the
         # step ends
@@ -262,7 +267,7 @@ def run_ours(args, wl):
             return outs
         outs, pending = [], []
         for x, lin in zip(xs, layers):
-            y = lin.local(x)
+            y = lin.local(x, one_call=one_call)
             if not distributed:
                 outs.append(y)
             elif equal_shards:
@@ -333,6 +338,18 @@ def run_ours(args, wl):
     launches = launches_per_step * args.steps
     fl = flops_per_step(wl)
     value = fl * args.steps / (ms * 1e-3) / 1e12
+    fused_linear = None
+    if not distributed and not one_call and not args.no_sweep:
+        # the same step with the quantizer inside the GEMM kernel (one kernel per linear), for comparison
+        ckb.set_tuning(4, 1)
+        replay_f, _ = graphed(lambda: step(one_call=True))
+        for _ in range(warm):
+            replay_f()
+        ms_f = timed(replay_f, args.steps)
+        ckb.set_tuning(4, 0)
+        fused_linear = {"ms_per_step": ms_f / args.steps, "value": fl * args.steps / (ms_f * 1e-3) / 1e12,
+                        "what": "ck_b200_linear_nvfp4 with the activation quantizer inside the GEMM kernel "
+                                "(CK_B200_TUNE_LINEAR_FUSED), one CUDA graph per step"}
 
     # ---- per-kernel timing: the same K steps with only the GEMMs, then only the quantizers, back to back ----
     qw = [(l.qweight, l.weight_block_scale, l.weight_scale) for l in layers]
@@ -604,11 +621,14 @@ def run_ours(args, wl):
                                          "barrier kernel before and after the step") if fused else
                                         ", NCCL all-gather of bf16 outputs (overlapping the next linear)" if distributed else ""),
                        "launch": "one CUDA graph per step" if use_graph else "eager launches",
+                       "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
+                                  "(ck_b200_linear_nvfp4)") if one_call and not distributed else
+                                 "quantize_nvfp4 kernel, then scaled_mm_nvfp4 kernel",
                        "l2": "no flush: one step touches ~0.6 GB (activations, packed operands, outputs), 5x the 126 MB L2"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
-            "quantize_sweep": sweep, "small_m_sweep": small_m, "mxfp8": mxfp8,
+            "quantize_sweep": sweep, "small_m_sweep": small_m, "mxfp8": mxfp8, "fused_linear": fused_linear,
         }
         if fused:
             # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate
@@ -641,6 +661,9 @@ def main():
                     help="N > 1: all-gather fused into the GEMM epilogue over peer memory, or a NCCL all-gather after it")
     ap.add_argument("--gemm-debug", action="store_true",
                     help="also launch each linear's GEMM once with in-kernel cycle counters (prints extra lines)")
+    ap.add_argument("--fused-linear", action="store_true",
+                    help="step = one kernel per linear (the GEMM kernel quantizes the activations) instead of "
+                         "quantize_nvfp4 and scaled_mm_nvfp4 as two kernels")
     ap.add_argument("--e2e-serial", action="store_true",
                     help="end-to-end arm: one host<->device transfer at a time instead of overlapping the two directions")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")

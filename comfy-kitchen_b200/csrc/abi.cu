@@ -11,7 +11,7 @@ std::atomic<int> g_quant_variant{2};
 std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
-std::atomic<int> g_linear_fused{1};
+std::atomic<int> g_linear_fused{0};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -190,7 +190,7 @@ int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, c
     }
     void* qx = ws + p.q_off;
     void* sfx = ws + p.sf_off;
-    // more than one tile row and column: the GEMM kernel quantizes the activations itself, beside its main loop
+    // on request, for more than one tile row and column: the GEMM kernel quantizes the activations itself
     if (ckb::g_linear_fused.load() && ckb::g_gemm_variant.load() == 0 &&
         ckb::fused_linear_supported(x_dtype, x_dev, M, N, K, out_dtype))
         return ckb::fused_linear_launch(x_dev, x_dtype, M, K, ts_x, qx, sfx, ws + p.sync_off, w_q_dev, w_sf_dev,

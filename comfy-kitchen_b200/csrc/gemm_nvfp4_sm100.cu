@@ -712,20 +712,24 @@ constexpr uint32_t kIdesc2Mx = ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((uin
 // by HBM, then runs beside the tensor-core main loop instead of in front of it.  Tiles are walked one row block
 // after the other, so the first wave of tiles needs only the first few 128-row bands and the quantizer warps (which
 // take the bands in the same order and never wait for anything) stay ahead of the loads from then on.
+// Measured on a B200 (M = 4608, eager launches): 3072 -> 9216 takes 66-68 us against 64-66 us for the quantizer kernel
+// followed by the GEMM kernel, 12288 -> 3072 takes 96-97 us against 87-89 us.  Eight warps per SM walk a segment at a
+// time (loads, arithmetic, stores, release, in sequence) and move about 1 TB/s where the stand-alone quantizer, with
+// 24 resident warps per SM, moves 4-5 TB/s; the producers then wait for bands (a quarter of their time) and the main
+// loop starves.  The path is therefore off by default (CK_B200_TUNE_LINEAR_FUSED) and kept for shapes and parts
+// where the balance differs; its results are bit-identical to the separate kernels.
 //
-// Progress is published per band in 64-bit words {epoch : count} in a small sync area of the caller's workspace.  A
-// word counts only while its upper half equals the current epoch, which the last CTA to leave the kernel advances,
-// so the words need no initialisation and no clean-up, and replays of a captured launch work like fresh ones.
-// A producer warp polls its band's word (bounded, like every wait here) before the first load of a tile, then
+// Progress is published per band as a counter in a small sync area of the caller's workspace, bumped with one
+// atomic add per finished segment.  The counters are zero when a kernel starts: the caller zeroes the area once, and
+// the last CTA to leave a kernel zeroes what the kernel used, so replays of a captured launch work like fresh ones.
+// A producer warp polls its band's counter (bounded, like every wait here) before the first load of a tile, then
 // orders its TMA loads after what it has seen with a proxy fence.  Calls that share a workspace must not overlap
 // on the GPU (they would also share the quantized operand).
 constexpr int kQuantWarps = 8;
 struct FusedQuantSync {
-    uint32_t epoch;
-    uint32_t pad;
-    unsigned long long exits;       // CTAs that have left the kernel
-    unsigned long long bands_done;  // bands completely quantized
-    unsigned long long band[1];     // [bands] warps done with their segment of the band
+    uint32_t exits;        // CTAs that have left the kernel
+    uint32_t bands_done;   // bands completely quantized
+    uint32_t band[2];      // [bands] warps done with their segment of the band
 };
 struct FusedQuant {
     QuantArgs q;
@@ -733,20 +737,9 @@ struct FusedQuant {
     int bands;
 };
 
-// Adds one to the count of *w for `epoch` (a word of another epoch counts as zero); returns the new count.
-__device__ __forceinline__ uint32_t epoch_arrive(unsigned long long* w, uint32_t epoch) {
-    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(w);
-    for (;;) {
-        const uint32_t count = ((uint32_t)(old >> 32) == epoch) ? (uint32_t)old : 0u;
-        const unsigned long long want = ((unsigned long long)epoch << 32) | (unsigned long long)(count + 1u);
-        const unsigned long long seen = atomicCAS(w, old, want);
-        if (seen == old) return count + 1u;
-        old = seen;
-    }
-}
-__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
@@ -827,12 +820,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);   // CTA 0's barriers
         bool q_all_ready = false;
         long long q_waited = 0;
-        unsigned long long q_band_target = 0, q_all_target = 0;
-        if (QF) {
-            const unsigned long long e = (unsigned long long)ld_relaxed_u32(&fq.sync->epoch) << 32;
-            q_band_target = e | (unsigned long long)(32 * fq.q.segments);
-            q_all_target = e | (unsigned long long)fq.bands;
-        }
+        const uint32_t q_band_target = QF ? (uint32_t)(32 * fq.q.segments) : 0u;
+        const uint32_t q_all_target = QF ? (uint32_t)fq.bands : 0u;
+        uint32_t q_pre_all = 0, q_pre_band = 0;
+        bool q_have_pre = false;
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
             int tm, tn;
             tile_coords(g, tile, tm, tn);
@@ -842,29 +833,31 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const int sfb_chunk0 = tn * 2 * g.sf_cbg;
             if (QF && !q_all_ready) {
                 // this CTA's A rows and their scales are one band of the activation matrix: wait until the
-                // quantizer warps (of any CTA) have finished it
+                // quantizer warps (of any CTA) have finished it.  The counters were read ahead while the previous
+                // tile's loads were in flight, so the common case costs no round trip to L2 here.
                 const int band = tm * 2 + (int)rank;
                 const long long t0 = now();
-                if (lane == 0) {
-                    if (ld_acquire_u64(&fq.sync->bands_done) == q_all_target) {
-                        q_all_ready = true;
-                    } else if (band < fq.bands) {
-                        const long long start = clock64();
-                        while (ld_acquire_u64(&fq.sync->band[band]) != q_band_target) {
-                            if (*abort_flag) { ok = false; break; }
-                            if (clock64() - start > WAIT_LIMIT_CYCLES) {
-                                *abort_flag = 1;
-                                atomicCAS(&g_device_status, 0, (int)WAIT_QUANT_BAND);
-                                ok = false;
-                                break;
-                            }
-                            __nanosleep(64);
+                const uint32_t all_v = q_have_pre ? q_pre_all : ld_relaxed_u32(&fq.sync->bands_done);
+                uint32_t band_v = q_band_target;
+                if (band < fq.bands) band_v = q_have_pre ? q_pre_band : ld_relaxed_u32(&fq.sync->band[band]);
+                if (all_v == q_all_target) {
+                    q_all_ready = true;
+                } else if (band_v != q_band_target) {
+                    const long long start = clock64();
+                    while (ld_relaxed_u32(&fq.sync->band[band]) != q_band_target) {
+                        if (*abort_flag) { ok = false; break; }
+                        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                            *abort_flag = 1;
+                            atomicCAS(&g_device_status, 0, (int)WAIT_QUANT_BAND);
+                            ok = false;
+                            break;
                         }
+                        __nanosleep(64);
                     }
-                    fence_proxy_async_all();   // the loads below read what the quantizer warps wrote with plain stores
                 }
-                q_all_ready = __shfl_sync(0xffffffffu, (int)q_all_ready, 0) != 0;
                 ok = __all_sync(0xffffffffu, ok);
+                __threadfence();           // acquire: pairs with the quantizer warps' release of the band
+                fence_proxy_async_all();   // the TMA loads below read what those warps wrote with plain stores
                 q_waited += now() - t0;
                 if (!ok) break;
             }
@@ -883,6 +876,19 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     tma_load_2d_pair(st + kA2 + kB2, &tmap_sfa, 0, sfa_chunk0 + kb * kSfChunks, bar);
                     tma_load_2d_pair(st + kA2 + kB2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + kb * kSfChunks, bar);
                     tma_load_2d_pair(st + kA2 + kB2 + kSfa2 + kSfa2, &tmap_sfb, 0, sfb_chunk0 + g.sf_cbg + kb * kSfChunks, bar);
+                }
+                if (QF && kb == 0 && !q_all_ready) {
+                    // read ahead the counters the next tile will ask for
+                    const int next = tile + num_pairs;
+                    q_have_pre = false;
+                    if (next < total_tiles) {
+                        int nm, nn;
+                        tile_coords(g, next, nm, nn);
+                        const int nb = nm * 2 + (int)rank;
+                        q_pre_all = ld_relaxed_u32(&fq.sync->bands_done);
+                        q_pre_band = nb < fq.bands ? ld_relaxed_u32(&fq.sync->band[nb]) : q_band_target;
+                        q_have_pre = true;
+                    }
                 }
                 __syncwarp();
                 if (++stage == kStages2) { stage = 0; phase ^= 1; }
@@ -987,7 +993,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         // ---------------- activation quantizer (eight warps of both CTAs) ----------------
         if constexpr (QF) {
             const long long t_begin = now();
-            const uint32_t epoch = ld_relaxed_u32(&fq.sync->epoch);
             const float ts = __ldg(fq.q.pts);
             const int per_band = 32 * fq.q.segments;
             const int items = fq.bands * per_band;
@@ -996,12 +1001,12 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const int band = item / per_band;
                 const int rem = item - band * per_band;
                 quantize_segment<QDT, true, 2>(fq.q, rem >> 5, band * 32 + (rem & 31), lane, ts);
-                __threadfence();
-                fence_proxy_async_all();
+                // release by one lane: the warp barrier orders the other lanes' stores before lane 0's fence, which
+                // is cumulative; the other lanes go on to the next segment's loads meanwhile
                 __syncwarp();
-                if (lane == 0 && epoch_arrive(&fq.sync->band[band], epoch) == (uint32_t)per_band) {
+                if (lane == 0) {
                     __threadfence();
-                    epoch_arrive(&fq.sync->bands_done, epoch);
+                    if (atomicAdd(&fq.sync->band[band], 1u) + 1u == (uint32_t)per_band) atomicAdd(&fq.sync->bands_done, 1u);
                 }
             }
             if (DBG && pair == 0 && threadIdx.x == NUM_THREADS)
@@ -1132,13 +1137,22 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
-    if (QF && threadIdx.x == 0) {
-        // every warp of this CTA is past its last use of the sync words; the last CTA out starts the next epoch
-        const uint32_t epoch = ld_relaxed_u32(&fq.sync->epoch);
-        __threadfence();
-        if (epoch_arrive(&fq.sync->exits, epoch) == gridDim.x) {
+    if (QF) {
+        // every warp of this CTA is past its last use of the counters; the last CTA out leaves them zero for the
+        // next kernel
+        __shared__ uint32_t s_last;
+        if (threadIdx.x == 0) {
             __threadfence();
-            atomicAdd(&fq.sync->epoch, 1u);
+            s_last = (atomicAdd(&fq.sync->exits, 1u) + 1u == gridDim.x) ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int i = threadIdx.x; i < fq.bands; i += blockDim.x) fq.sync->band[i] = 0u;
+            if (threadIdx.x == 0) {
+                fq.sync->bands_done = 0u;
+                fq.sync->exits = 0u;
+            }
         }
     }
 }
@@ -1542,7 +1556,7 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
 
 namespace ckb {
 constexpr size_t kFusedSyncBytes = 32768;
-constexpr int64_t kFusedMaxBands = (int64_t)(kFusedSyncBytes - sizeof(FusedQuantSync)) / 8;
+constexpr int64_t kFusedMaxBands = (int64_t)(kFusedSyncBytes - sizeof(FusedQuantSync)) / 4;
 size_t fused_sync_bytes() { return kFusedSyncBytes; }
 
 bool fused_linear_supported(int x_dtype, const void* x_dev, int64_t M, int64_t N, int64_t K, int out_dtype) {
@@ -1555,7 +1569,7 @@ int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, co
                         void* sfx_dev, void* sync_dev, const void* w_q_dev, const void* w_sf_dev,
                         const float* w_scale_dev, int64_t N, const void* bias_dev_or_null, int bias_dtype, void* out_dev,
                         int out_dtype, void* stream) {
-    if (!x_dev || !ts_x_dev || !qx_dev || !sfx_dev || !sync_dev || ((uintptr_t)sync_dev & 7))
+    if (!x_dev || !ts_x_dev || !qx_dev || !sfx_dev || !sync_dev || ((uintptr_t)sync_dev & 3))
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused linear: null or misaligned pointer");
     FusedQuant fq;
     QuantArgs& a = fq.q;

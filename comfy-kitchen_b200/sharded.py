@@ -202,8 +202,13 @@ class ShardedNVFP4Linear:
         self.input_scale = None if inp is None else inp.to(device=dev, dtype=torch.float32).reshape(())
         return self
 
-    def local(self, x: torch.Tensor) -> torch.Tensor:
-        """This rank's [M, n1-n0] block of the output."""
+    def local(self, x: torch.Tensor, one_call: bool = False) -> torch.Tensor:
+        """This rank's [M, n1-n0] block of the output.  ``one_call``: through the library's whole-linear entry point
+        (same bits; for more than 128 rows and columns the GEMM kernel then quantizes x itself)."""
+        if one_call and hasattr(self.ops, "linear_nvfp4") and x.dtype in (torch.float16, torch.bfloat16):
+            y = self.ops.linear_nvfp4(x, self.qweight, self.weight_block_scale, self.weight_scale,
+                                      input_scale=self.input_scale, bias=self.bias)
+            return y[:, : self.local_rows]
         ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
         pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
         qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)

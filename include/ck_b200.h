@@ -159,13 +159,13 @@ int ck_b200_peer_free(void* ptr);
  *   workspace_dev: 256-byte aligned, at least ck_b200_linear_nvfp4_workspace_bytes(M, K) bytes; anything beyond that
  *   (1 MiB or more) is used for the split-K reduction when M <= 128
  *
- * With M > 128, N > 128 and bf16 / fp16 activations the call is ONE kernel: the CTA-pair GEMM carries eight extra
- * warps per CTA that quantize x into the workspace while the tensor-core main loop runs, and each tile's loads wait
- * (bounded) for the 128-row band of x they read.  Results are bit-identical to the separate operators.  The progress
+ * Optional (CK_B200_TUNE_LINEAR_FUSED = 1; off by default because it measured slower on B200): with M > 128, N > 128
+ * and bf16 / fp16 activations the call is ONE kernel: the CTA-pair GEMM carries eight extra warps per CTA that
+ * quantize x into the workspace while the tensor-core main loop runs, and each tile's loads wait (bounded) for the
+ * 128-row band of x they read.  Results are bit-identical to the separate operators.  The progress
  * words live in bytes [256, 256 + 32 KiB) of the workspace, which only that kernel writes: zero them once when the
  * workspace is allocated (they then stay consistent over any sequence of calls, shapes and graph replays).  Calls
  * that share a workspace must not overlap on the GPU.
- * CK_B200_TUNE_LINEAR_FUSED = 0 switches back to separate quantizer and GEMM kernels.
  */
 int64_t ck_b200_linear_nvfp4_workspace_bytes(int64_t M, int64_t K);
 int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* input_scale_dev_or_null,
@@ -229,8 +229,8 @@ int ck_b200_read_device_status(int* status_out);
 #define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the GEMM kernel's first CTA prints the cycles its roles spent waiting */
 #define CK_B200_TUNE_DEPENDENT_LAUNCH 3 /* non-zero (default): kernels are launched with programmatic stream
                                           serialisation, so a kernel's set-up overlaps the previous kernel's tail */
-#define CK_B200_TUNE_LINEAR_FUSED 4  /* non-zero (default): ck_b200_linear_nvfp4 quantizes the activations inside the
-                                        GEMM kernel when the shape allows it */
+#define CK_B200_TUNE_LINEAR_FUSED 4  /* non-zero: ck_b200_linear_nvfp4 quantizes the activations inside the GEMM kernel
+                                        when the shape allows it (default 0: separate kernels, which measured faster) */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus

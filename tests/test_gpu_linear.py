@@ -79,6 +79,15 @@ def test_linear_quantizer_inside_the_gemm(dtype):
     bit-identical to the separate operators, over a sequence of shapes that share the workspace (rows that are not
     multiples of 16 or 128, K that is not a multiple of 128), with a dynamic and with a static activation scale."""
     import comfy_kitchen_b200 as ckb
+    old = ckb.set_tuning(4, 1)
+    try:
+        _fused_shapes(ckb, dtype)
+    finally:
+        ckb.set_tuning(4, old)
+    assert ckb.read_device_status() == 0
+
+
+def _fused_shapes(ckb, dtype):
     for i, (M, N, K) in enumerate(FUSED_SHAPES * 2):
         w = seeded_randn((N, K), seed=20 + i, std=0.02).cuda()
         b = seeded_randn((1, N), seed=40 + i, std=0.1, dtype=dtype).reshape(N).cuda()
@@ -89,10 +98,9 @@ def test_linear_quantizer_inside_the_gemm(dtype):
         for _ in range(3):
             got = lin(x)
             assert got.dtype == dtype and torch.equal(got, want), f"{M}x{N}x{K}: fused linear differs"
-    assert ckb.read_device_status() == 0
 
 
-def test_linear_quantizer_inside_the_gemm_can_be_switched_off_and_replayed():
+def test_linear_quantizer_inside_the_gemm_is_opt_in_and_replays():
     import comfy_kitchen_b200 as ckb
     M, N, K = 1024, 1024, 2048
     w = seeded_randn((N, K), seed=81, std=0.02).cuda()
@@ -100,17 +108,22 @@ def test_linear_quantizer_inside_the_gemm_can_be_switched_off_and_replayed():
     lin = ckb.NVFP4Linear.from_float(w, None, input_scale=torch.tensor(0.02))
     want = lin.forward_unfused(x)
     n0 = ckb.launches()
+    assert torch.equal(lin(x), want)
+    assert ckb.launches() - n0 == 2, "default: quantizer kernel, then GEMM kernel"
+    old = ckb.set_tuning(4, 1)
+    try:
+        _fused_one_kernel_and_replays(ckb, lin, x, want, M, K)
+    finally:
+        ckb.set_tuning(4, old)
+    assert ckb.read_device_status() == 0
+
+
+def _fused_one_kernel_and_replays(ckb, lin, x, want, M, K):
+    n0 = ckb.launches()
     y = lin(x)
     assert ckb.launches() - n0 == 1, "the fused linear is one kernel when the activation scale is static"
     assert torch.equal(y, want)
-    old = ckb.set_tuning(4, 0)
-    try:
-        n0 = ckb.launches()
-        assert torch.equal(lin(x), want)
-        assert ckb.launches() - n0 == 2
-    finally:
-        ckb.set_tuning(4, old)
-    # replays of a captured call: the progress words carry over from one replay to the next
+    # replays of a captured call: the progress counters are left at zero by each replay
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         lin(x)
