@@ -12,6 +12,7 @@ std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
 std::atomic<int> g_linear_fused{0};
+std::atomic<int> g_quant_flat{12};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -93,6 +94,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_GEMM_VARIANT: return ckb::g_gemm_variant.exchange(value);
         case CK_B200_TUNE_GEMM_DEBUG: return ckb::g_gemm_debug.exchange(value);
         case CK_B200_TUNE_LINEAR_FUSED: return ckb::g_linear_fused.exchange(value);
+        case CK_B200_TUNE_QUANT_FLAT: return ckb::g_quant_flat.exchange(value);
         default: return -1;
     }
 }

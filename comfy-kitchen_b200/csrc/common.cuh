@@ -31,6 +31,7 @@ int check_device(int* sm_count_out);
 // The CTA-pair GEMM with the activation quantizer inside (gemm_nvfp4_sm100.cu): whether a linear can take that
 // path, the bytes of its sync area, and the launch.  qx / sfx receive the quantized activations (rows padded to 16).
 extern std::atomic<int> g_linear_fused;
+extern std::atomic<int> g_quant_flat;   // 0 = off, else the least units per warp for the one-wave quantizer geometry
 bool fused_linear_supported(int x_dtype, const void* x_dev, int64_t M, int64_t N, int64_t K, int out_dtype);
 size_t fused_sync_bytes();
 int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* ts_x_dev, void* qx_dev,

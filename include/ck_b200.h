@@ -231,6 +231,8 @@ int ck_b200_read_device_status(int* status_out);
                                           serialisation, so a kernel's set-up overlaps the previous kernel's tail */
 #define CK_B200_TUNE_LINEAR_FUSED 4  /* non-zero: ck_b200_linear_nvfp4 quantizes the activations inside the GEMM kernel
                                         when the shape allows it (default 0: separate kernels, which measured faster) */
+#define CK_B200_TUNE_QUANT_FLAT 5     /* quantize_nvfp4 launch geometry: 0 = segments of rows in several waves; n > 0
+                                        (default 12) = one wave of equal ranges when every resident warp gets n to 128 units */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus
