@@ -251,6 +251,16 @@ def run_ours(args, wl):
     if fused and not (equal_shards and M > 128 and all(n // world > 128 for _, _, n in wl["linears"])):
         fused = False            # the fused kernel wants equal shards wider than 128 columns and more than 128 rows
         use_graph = False
+    # The fused path maps every rank's output matrices into every process.  With 18 GB of peer mappings (the Wan
+    # workload on 8 GPUs: 7 peers x 2.6 GB) its stores ran at 96 GB/s per rank, 23.4 ms per step, where the NCCL
+    # all-gather, which stages through small buffers, took 4.1 ms; with 1.8 GB (Flux, 8 GPUs) and 2.6 GB (Wan, 2 GPUs)
+    # the fused path ran at 420-480 GB/s.  Large footprints therefore take the NCCL path.
+    peer_bytes = (world - 1) * sum(M * n * 2 for _, _, n in wl["linears"])
+    fused_declined = None
+    if fused and peer_bytes > (4 << 30):
+        fused = False
+        use_graph = False
+        fused_declined = f"{peer_bytes / 2**30:.1f} GiB of peer-mapped output matrices per rank: NCCL all-gather instead"
     if fused:
         peers = ckb.PeerGroup(dev)
         for lin in layers:
@@ -619,7 +629,8 @@ def run_ours(args, wl):
             "config": {"workload": wl["name"], "M": M, "linears": wl["linears"],
                        "parallelism": f"weights N-sharded over {world} GPU(s)" + ((", all-gather of bf16 outputs fused into the GEMM epilogue (stores to peer memory over NVLink), "
                                          "barrier kernel before and after the step") if fused else
-                                        ", NCCL all-gather of bf16 outputs (overlapping the next linear)" if distributed else ""),
+                                        ", NCCL all-gather of bf16 outputs (overlapping the next linear)"
+                                        + (f" [{fused_declined}]" if fused_declined else "") if distributed else ""),
                        "launch": "one CUDA graph per step" if use_graph else "eager launches",
                        "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
                                   "(ck_b200_linear_nvfp4)") if one_call and not distributed else
