@@ -1300,14 +1300,15 @@ int max_active_pairs(int* out) {
     constexpr int kThreads = QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS;
     static std::mutex mu;
     static int cache[64] = {0};
-    int dev = 0;
+    int dev = 0, sms = 0;
     CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (int rc = check_device(&sms)) return rc;   // also bounds the device ordinal
     std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == 0) {
         auto kernel = gemm_nvfp4_pair_kernel<KB, false, 0, QDT>;
         CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * 148);
+        cfg.gridDim = dim3(2 * (unsigned)sms);
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = kSmemBytes2;
         cudaLaunchAttribute attr;

@@ -415,5 +415,7 @@ def launches() -> int:
 def read_device_status() -> int:
     """Synchronises and returns the device status word (0 = no bounded wait ran out), clearing it."""
     v = ctypes.c_int(0)
-    _lib.load().ck_b200_read_device_status(ctypes.byref(v))
+    rc = _lib.load().ck_b200_read_device_status(ctypes.byref(v))
+    if rc not in (0, 4):      # 4 = CK_B200_ERR_DEVICE_STATUS: the word itself says which wait ran out
+        _lib.check(rc, "read_device_status")
     return int(v.value)

@@ -134,7 +134,8 @@ def test_gemm_first_config_golden(ckb, golden_large, oracle, variant):
 
 
 FLUX = [(4608, 9216, 3072), (4608, 3072, 3072), (4608, 12288, 3072), (4608, 3072, 12288)]
-WAN_T5 = [(32760, 5120, 5120), (32760, 13824, 5120), (512, 10240, 4096), (64, 4096, 10240), (16, 10240, 4096)]
+WAN_T5 = [(32760, 15360, 5120), (32760, 5120, 5120), (32760, 13824, 5120), (32760, 5120, 13824), (512, 10240, 4096),
+          (64, 4096, 10240), (16, 10240, 4096)]
 
 
 @pytest.mark.parametrize("mnk", FLUX + WAN_T5, ids=lambda s: "x".join(map(str, s)))

@@ -192,6 +192,34 @@ def test_full_size_properties(ckb):
     assert torch.equal(sfl.view(torch.uint8), sf.view(torch.uint8)[:8192])
 
 
+SWEEP = [(m, k) for m in (1024, 4096, 16384, 65536) for k in (3072, 5120, 12288)]
+
+
+@pytest.mark.parametrize("mk", SWEEP, ids=lambda s: "x".join(map(str, s)))
+def test_sweep_shapes_row_slices_vs_oracle(mk, ckb, oracle):
+    """Every shape of the bandwidth-sweep configuration: the first, middle and last 256 rows of the whole-tensor
+    result against the CPU oracle on those rows, bytes, scales and the bf16 round trip (the block scales depend on the
+    row only, and 256 rows are two whole 128-row scale bands, so the slice of the result is the result of the slice)."""
+    M, K = mk
+    g = torch.Generator(device="cuda").manual_seed(M * 31 + K)
+    x = torch.randn((M, K), generator=g, device="cuda", dtype=torch.bfloat16)
+    ts = ckb.dynamic_scale_nvfp4(x)
+    tsf = float(ts.item())
+    assert np.float32(tsf) == np.float32(float((x.abs().amax() / 2688.0).float()))    # bf16 arithmetic, like the layout
+    q, sf = ckb.quantize_nvfp4(x, ts)
+    y = ckb.dequantize_nvfp4(q, ts, sf, torch.bfloat16)
+    sfu = sf.view(torch.uint8)
+    for r0 in sorted({0, (M // 2) // 128 * 128, M - 256}):
+        xb = to_bits(x[r0:r0 + 256])
+        q_ref, sf_ref = oracle.quantize_nvfp4(xb, oracle.BF16, tsf)
+        assert np.array_equal(to_bits(q[r0:r0 + 256]), q_ref), f"packed bytes differ in rows {r0}..{r0 + 255}"
+        assert np.array_equal(to_bits(sfu[r0:r0 + 256]), sf_ref), f"scale bytes differ in rows {r0}..{r0 + 255}"
+        y_ref = oracle.dequantize_nvfp4(q_ref, tsf, sf_ref, oracle.BF16)
+        assert np.array_equal(to_bits(y[r0:r0 + 256]), y_ref), f"round trip differs in rows {r0}..{r0 + 255}"
+    del x, q, sf, y
+    torch.cuda.empty_cache()
+
+
 def test_first_config_digests(ckb, golden_large, oracle):
     import hashlib
     rng = np.random.default_rng(0)
