@@ -12,20 +12,23 @@ N(0,1) with 0.1 % of the channels scaled x20, weights N(0,0.02)); no model weigh
 Prints ONE JSON line.  `value` is whole-job TFLOP/s (2*M*N*K summed over the linears / step time, device
 resident inputs); `e2e` is the same metric with pinned host inputs and host outputs, copies inside the timed
 region; `roofline` describes the dominant kernel (the GEMM); `cpu_baseline` is the CPU oracle timed on a
-bounded sample of the same workload on this box's host cores.
+bounded sample of the same workload on this box's host cores.  Beside them: `parity` (the results of the timed
+path checked inside this run), `sustained` (the step replayed for seconds, with the clocks seen), `fp4_ceiling`
+(cuBLASLt's NVFP4 kernel on 8192^3 and 16384^3, the measured ceiling the GEMM fractions are also given against),
+`wan` (a short record of the Wan-class workload, the one whose weights are sharded over the GPUs), the quantizer
+sweep (L2-cold and L2-warm), comparators for the quantizer, and the small-M and MXFP8 records.
 
 With --gpus N > 1 (launched under torchrun, one rank per GPU) every weight is sharded along N, each rank
-multiplies its shard and the bf16 column blocks are all-gathered over NCCL: total work is fixed ("strong").
+multiplies its shard and the bf16 column blocks are all-gathered: total work is fixed ("strong").
 `--impl reference` times the CPU restatement of the reference eager path (the oracle) as the reference arm.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
-import subprocess
 import sys
-import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -36,15 +39,27 @@ FLUX = {"name": "flux_dit_block_linears", "M": 4608,
 WAN = {"name": "wan14b_dit_block_linears", "M": 32760,
        "linears": [("qkv", 5120, 15360), ("attn_out", 5120, 5120), ("ffn_up", 5120, 13824), ("ffn_down", 13824, 5120)]}
 WORKLOADS = {"flux": FLUX, "wan": WAN}
-NOMINAL_NVFP4_TFLOPS = 9000.0   # vendor dense NVFP4 figure for B200; MEASURED_PEAKS.json holds no FP4 number
+NOMINAL_NVFP4_TFLOPS = 9000.0   # vendor dense NVFP4 figure for B200
 METRIC = "scaled_mm_nvfp4 TFLOPS over the NVFP4 linear path (quantize_nvfp4 + scaled_mm_nvfp4 per linear)"
+DTYPE = "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate"
+SWEEP_SHAPES = [(m, k) for m in (1024, 4096, 16384, 65536) for k in (3072, 5120, 12288)]
+L2_BYTES = 126 << 20
+CPU_SAMPLE_ROWS = 1152
 
 
 def flops_per_step(wl) -> float:
     return sum(2.0 * wl["M"] * n * k for _, k, n in wl["linears"])
 
 
-def make_inputs(wl, device, dtype):
+def workload_config(wl) -> dict:
+    """The `config` of the JSON line: what is computed, identical in both arms."""
+    return {"workload": wl["name"], "M": wl["M"], "linears": [list(l) for l in wl["linears"]],
+            "input_scale": "static per-tensor activation scales (amax/(448*6) of each activation, computed once "
+                           "before the timed region, like the input_scale of an NVFP4 checkpoint)",
+            "l2": "no flush: one step touches ~0.6 GB (activations, packed operands, outputs), 5x the 126 MB L2"}
+
+
+def make_inputs(wl, dtype):
     """Seeded activations and weights, generated on the CPU so that every rank and the CPU arm see the same bits."""
     import torch
     xs, ws = [], []
@@ -59,6 +74,24 @@ def make_inputs(wl, device, dtype):
     return xs, ws
 
 
+def make_inputs_on_device(wl, dev, dtype):
+    """The same distributions from a seeded generator of the device (identical on every rank: same GPU model, same
+    seed); used for the Wan-class record, whose 0.9 GB activations would take the host tens of seconds."""
+    import torch
+    xs, ws = [], []
+    for i, (_, k, n) in enumerate(wl["linears"]):
+        g = torch.Generator(device=dev).manual_seed(2000 + i)
+        x = torch.randn((wl["M"], k), generator=g, device=dev, dtype=torch.float32)
+        cols = torch.randperm(k, generator=g, device=dev)[: max(1, round(k / 1000))]
+        x[:, cols] *= 20.0
+        xs.append(x.to(dtype))
+        del x
+        w = torch.randn((n, k), generator=g, device=dev, dtype=torch.float32) * 0.02
+        ws.append(w.to(dtype))
+        del w
+    return xs, ws
+
+
 class ClockSampler:
     """SM clock and throttle-reason samples taken through NVML (read-only) by a thread while the GPU is under load."""
 
@@ -66,6 +99,7 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.period_s = period_s
         self.samples = []
+        self.power = []
         self.reasons = 0
         self.max_mhz = None
         self._stop = False
@@ -77,11 +111,11 @@ class ClockSampler:
             import threading
 
             import pynvml
+            import torch
             pynvml.nvmlInit()
             # torch's device ordinal follows CUDA_VISIBLE_DEVICES; map it to the NVML handle through the PCI bus id
-            import torch
-            bus = torch.cuda.get_device_properties(self.gpu_index).pci_bus_id if hasattr(
-                torch.cuda.get_device_properties(self.gpu_index), "pci_bus_id") else None
+            props = torch.cuda.get_device_properties(self.gpu_index)
+            bus = props.pci_bus_id if hasattr(props, "pci_bus_id") else None
             handle = None
             if bus is not None:
                 for i in range(pynvml.nvmlDeviceGetCount()):
@@ -99,6 +133,7 @@ class ClockSampler:
                     try:
                         self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
                         self.reasons |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                        self.power.append(pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0)
                     except Exception:
                         pass
                     time.sleep(self.period_s)
@@ -107,6 +142,7 @@ class ClockSampler:
             self._thread.start()
         except Exception:
             self._thread = None
+        return self
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
@@ -124,6 +160,9 @@ class ClockSampler:
         if self.samples:
             sm = sorted(self.samples)
             out.update(sm_mhz=sm[len(sm) // 2], samples=len(sm), sm_min_mhz=sm[0], sm_p90_mhz=sm[int(len(sm) * 0.9)])
+        if self.power:
+            pw = sorted(self.power)
+            out.update(power_w_median=pw[len(pw) // 2], power_w_max=pw[-1])
         return out
 
 
@@ -155,6 +194,7 @@ def prepare_cpu(wl, xs, ws):
     import torch
     from oracle import oracle as o
     o.build()
+    threads = o.use_all_cores()    # explicit: a launcher's OMP_NUM_THREADS=1 must not shrink the baseline
     xs_bits, w_q = [], []
     for x, w in zip(xs, ws):
         xb = x.view(torch.int16).numpy().view(np.uint16)
@@ -164,7 +204,11 @@ def prepare_cpu(wl, xs, ws):
         qw, sfw = o.quantize_nvfp4(wb, o.BF16, ts_w)
         xs_bits.append((xb, ts_x))
         w_q.append((qw, sfw, ts_w))
-    return xs_bits, w_q, o.num_threads()
+    return xs_bits, w_q, threads
+
+
+def cpu_sample_text(wl, rows):
+    return f"first {rows} of {wl['M']} tokens of each of the {len(wl['linears'])} linears per step"
 
 
 def run_reference_arm(args, wl):
@@ -173,9 +217,9 @@ def run_reference_arm(args, wl):
     if rank != 0:
         return
     torch.manual_seed(0)
-    xs, ws = make_inputs(wl, "cpu", torch.bfloat16)
+    xs, ws = make_inputs(wl, torch.bfloat16)
     xs_bits, w_q, threads = prepare_cpu(wl, xs, ws)
-    rows = min(1152, wl["M"])
+    rows = min(CPU_SAMPLE_ROWS, wl["M"])
     for _ in range(max(1, args.warmup)):
         cpu_reference_step(wl, xs_bits, w_q, rows)
     t0 = time.perf_counter()
@@ -184,15 +228,15 @@ def run_reference_arm(args, wl):
         fl += cpu_reference_step(wl, xs_bits, w_q, rows)
     dt = time.perf_counter() - t0
     val = fl / dt / 1e12
-    sample = f"first {rows} of {wl['M']} tokens of each of the {len(wl['linears'])} linears per step"
+    sample = cpu_sample_text(wl, rows)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate",
-        "data": "synthetic", "config": {"workload": wl["name"], "M": wl["M"], "linears": wl["linears"], "sample": sample},
+        "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": workload_config(wl),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "run": {"sample": sample, "threads": threads, "omp_num_threads_env": os.environ.get("OMP_NUM_THREADS")},
         "note": "CPU restatement of the reference eager path (quantize_nvfp4 eager; scaled_mm_nvfp4 = dequantize to "
                 "fp32 + fp32 BLAS matmul, the check the reference's own tests use since its eager GEMM has no CPU kernel)",
     }
@@ -202,160 +246,663 @@ def run_reference_arm(args, wl):
 # ------------------------------------------------------------------------------------------------ GPU arm
 
 
+class Bench:
+    """Device, ranks and the timing helpers shared by every record of the GPU arm."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.args = torch, dist, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: comfy_kitchen_b200 has no CPU path")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.distributed = self.world > 1
+        if self.distributed:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.side = torch.cuda.Stream()       # capture stream
+        self.side2 = torch.cuda.Stream()      # second branch of a captured step (the quantizers)
+        self.graphs = []
+        self.use_graph = not args.no_graph
+
+    def barrier(self):
+        if self.distributed:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def graphed(self, fn, use_graph=None):
+        """Capture fn once (after warm-up on the capture stream) and return (replay, launches per replay)."""
+        import comfy_kitchen_b200 as ckb
+        torch = self.torch
+        if not (self.use_graph if use_graph is None else use_graph):
+            n0 = ckb.launches()
+            fn()
+            return fn, ckb.launches() - n0
+        with torch.cuda.stream(self.side):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        n0 = ckb.launches()
+        with torch.cuda.graph(g, stream=self.side):
+            keep = fn()
+        n = ckb.launches() - n0
+        g._keep = keep
+        self.graphs.append(g)
+        return g.replay, n
+
+    def timed(self, replay, reps, all_ranks=True):
+        """reps back-to-back replays between two CUDA events on the current stream; returns ms in total (the maximum
+        over the ranks when every rank takes part)."""
+        torch = self.torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if all_ranks:
+            self.barrier()
+        else:
+            torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            replay()
+        b.record()
+        if all_ranks:
+            self.barrier()
+        else:
+            torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        if self.distributed and all_ranks:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def for_seconds(self, replay, seconds, chunk):
+        """Replays in chunks until `seconds` have passed; returns (ms in total, replays), single-rank helper."""
+        torch = self.torch
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        a.record()
+        n = 0
+        while True:
+            for _ in range(chunk):
+                replay()
+            n += chunk
+            torch.cuda.synchronize()
+            if time.perf_counter() - t0 >= seconds:
+                break
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b), n
+
+
+def cublaslt_nvfp4(torch, q, sf, t, w_q, w_sf, w_ts):
+    """cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend
+    (comfy_kitchen/backends/eager/quantization.py:225-249)."""
+    from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+    return scaled_mm(q.view(torch.float4_e2m1fn_x2), w_q.view(torch.float4_e2m1fn_x2).t(),
+                     scale_a=[sf.view(-1), t.reshape(())], scale_b=[w_sf.view(-1), w_ts.reshape(())],
+                     scale_recipe_a=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+                     scale_recipe_b=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
+                     swizzle_a=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
+                     swizzle_b=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
+                     output_dtype=torch.bfloat16)
+
+
+def rel_rms(y, ref) -> float:
+    y, ref = y.double(), ref.double()
+    return float((y - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-30))
+
+
+class StepPlan:
+    """The layers of one workload on this rank and the ways a step over them can be enqueued."""
+
+    def __init__(self, B: Bench, wl, xs, ws, collective: str):
+        import comfy_kitchen_b200 as ckb
+        torch = B.torch
+        self.B, self.wl, self.ckb = B, wl, ckb
+        self.M = wl["M"]
+        self.xs = xs
+        # static per-tensor activation scales (the optional `input_scale` of an NVFP4 checkpoint), amax/(448*6)
+        self.ts_x = [ckb.dynamic_scale_nvfp4(x) for x in xs]
+        self.layers = [ckb.ShardedNVFP4Linear(w.to(B.dev), None, input_scale=t) for w, t in zip(ws, self.ts_x)]
+        torch.cuda.synchronize()
+        world, M = B.world, self.M
+        self.equal_shards = all(n % (8 * world) == 0 for _, _, n in wl["linears"])
+        self.fused = B.distributed and collective == "fused"
+        self.declined = None
+        if self.fused and not (self.equal_shards and M > 128 and all(n // world > 128 for _, _, n in wl["linears"])):
+            self.fused = False
+            self.declined = "the fused kernel wants equal shards wider than 128 columns and more than 128 rows"
+        # The fused path maps every rank's output matrices into every process.  With 18 GB of peer mappings (the
+        # Wan workload on 8 GPUs: 7 peers x 2.6 GB) its stores ran at 96 GB/s per rank; with 1.8 GB (Flux, 8 GPUs) and
+        # 2.6 GB (Wan, 2 GPUs) at 420-480 GB/s.  Large footprints therefore take the NCCL path, and the line says so.
+        peer_bytes = (world - 1) * sum(M * n * 2 for _, _, n in wl["linears"])
+        if self.fused and peer_bytes > (B.args.peer_map_limit_gib << 30):
+            self.fused = False
+            self.declined = (f"{peer_bytes / 2**30:.1f} GiB of peer-mapped output matrices per rank: NCCL all-gather "
+                             "instead")
+        self.use_graph = B.use_graph and (not B.distributed or self.fused)
+        self.peers = None
+        if self.fused:
+            self.peers = ckb.PeerGroup(B.dev)
+            for lin in self.layers:
+                lin.bind(self.peers, M)
+
+    def close(self):
+        if self.peers is not None:
+            self.peers.close()
+            self.peers = None
+
+    def mode_text(self):
+        B = self.B
+        if not B.distributed:
+            return "1 GPU"
+        if self.fused:
+            return (f"weights N-sharded over {B.world} GPUs, all-gather of bf16 outputs fused into the GEMM epilogue "
+                    "(stores to peer memory over NVLink), barrier kernel before and after the step")
+        return (f"weights N-sharded over {B.world} GPUs, NCCL all-gather of bf16 outputs (overlapping the next linear)"
+                + (f" [{self.declined}]" if self.declined else ""))
+
+    def step(self, one_call=False, dynamic=False):
+        """The linears one after the other on the current stream."""
+        B, layers, xs = self.B, self.layers, self.xs
+        if dynamic:      # per-call activation scale (the layer's default when a checkpoint has no input_scale)
+            saved = [l.input_scale for l in layers]
+            for l in layers:
+                l.input_scale = None
+        try:
+            if self.fused:
+                self.peers.barrier()                       # every rank is done with the previous step's matrices
+                outs = [lin.fused(x) for x, lin in zip(xs, layers)]
+                self.peers.barrier()                       # every rank's column blocks have arrived
+                return outs
+            outs, pending = [], []
+            for x, lin in zip(xs, layers):
+                y = lin.local(x, one_call=one_call)
+                if not B.distributed:
+                    outs.append(y)
+                elif self.equal_shards:
+                    work, buf = lin.gather_async(y)
+                    pending.append(work)
+                    outs.append(buf)
+                else:
+                    outs.append(lin.gather(y, row_major=False))
+            for work in pending:
+                work.wait()
+            return outs
+        finally:
+            if dynamic:
+                for l, s in zip(layers, saved):
+                    l.input_scale = s
+
+    def step_overlapped(self):
+        """The same work as two branches (captured into one CUDA graph): the quantizers run on a second stream, so
+        the quantizer of linear i+1 overlaps the GEMM (and, on several GPUs, the peer stores) of linear i.  Legitimate
+        because the four linears of the step are independent work items; inside a real block, where each linear's
+        input depends on the previous output, only the serial step applies."""
+        torch = self.B.torch
+        cur, qs = torch.cuda.current_stream(), self.B.side2
+        qs.wait_stream(cur)
+        quant, events = [], []
+        with torch.cuda.stream(qs):
+            for x, lin in zip(self.xs, self.layers):
+                quant.append(lin.quantize_input(x))
+                e = torch.cuda.Event()
+                e.record(qs)
+                events.append(e)
+        if self.fused:
+            self.peers.barrier()
+        outs = []
+        for (qx, sfx, t), lin, e in zip(quant, self.layers, events):
+            cur.wait_event(e)
+            outs.append(lin.fused_from_quantized(qx, sfx, t, self.M) if self.fused
+                        else lin.local_from_quantized(qx, sfx, t, self.M))
+        cur.wait_stream(qs)
+        if self.fused:
+            self.peers.barrier()
+        return outs, quant
+
+    def check_parity(self):
+        """The results of the path that is timed, checked inside this run.  Several GPUs: every rank's fused matrix
+        against the NCCL all-gather of the same column blocks, bit for bit, on every rank.  One GPU: each linear
+        against cuBLASLt's NVFP4 kernel on the same quantized operands (relative RMS error, tolerance 1e-2)."""
+        B, torch, ckb = self.B, self.B.torch, self.ckb
+        out = {}
+        if self.fused:
+            self.peers.barrier()
+            fused_out = [lin.fused(x) for x, lin in zip(self.xs, self.layers)]
+            self.peers.barrier()
+            torch.cuda.synchronize()
+            ok = 1
+            for x, lin, got in zip(self.xs, self.layers, fused_out):
+                want = lin.gather(lin.local(x))          # NCCL all-gather, row-major [M, N]; own memory only
+                if not torch.equal(got, want):
+                    ok = 0
+            flag = torch.tensor([ok], device=B.dev)
+            B.dist.all_reduce(flag, op=B.dist.ReduceOp.MIN)
+            all_ok = int(flag.item()) == 1
+            out = {"multi_gpu": "bit-equal to NCCL all-gather" if all_ok else "MISMATCH against NCCL all-gather",
+                   "ranks": B.world, "linears_checked": len(self.layers), "ok": all_ok}
+        elif not B.distributed:
+            errs = {}
+            try:
+                for (name, _, _), x, lin, t in zip(self.wl["linears"], self.xs, self.layers, self.ts_x):
+                    qx, sfx, _ = lin.quantize_input(x)
+                    y = lin.local_from_quantized(qx, sfx, t, self.M)
+                    ref = cublaslt_nvfp4(torch, qx, sfx, t, lin.qweight, lin.weight_block_scale, lin.weight_scale)
+                    errs[name] = rel_rms(y.float(), ref[: self.M].float())
+                    del y, ref
+                out = {"gemm_rel_rms_vs_cublaslt": errs, "tolerance": 1e-2, "ok": max(errs.values()) <= 1e-2}
+            except Exception as ex:   # depends on the torch / cuBLASLt build
+                out = {"gemm_rel_rms_vs_cublaslt": None, "unavailable": f"{type(ex).__name__}: {ex}"[:160], "ok": True}
+        else:
+            out = {"multi_gpu": "NCCL all-gather path (library collective): nothing fused to check", "ranks": B.world,
+                   "ok": True}
+        return out
+
+
+def reference_package():
+    """The copy of the reference's Python package under baseline/_ref (comparators only), or None."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "comfy_kitchen")):
+        return None
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    sys.dont_write_bytecode = True
+    try:
+        import comfy_kitchen as ck
+        return ck
+    except Exception:
+        return None
+
+
+def quantize_comparators(B: Bench, xs, ts_x, names):
+    """The reference's own GPU quantizers on the activations of the step, beside this library's: its Triton kernel
+    (comfy_kitchen/backends/triton/quantization.py:333-415, run from the copy of the reference's Python package) and
+    its CUDA kernel (comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:323-384, compiled by itself), each with GB/s
+    (2.5625 algorithmic bytes per element) and the number of output bytes that differ from the reference eager
+    backend on the same tensor.  Eager is the contract; this library's count is zero."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    ck = reference_package()
+    if ck is None:
+        return {"unavailable": "baseline/_ref/comfy_kitchen is absent (baseline/make_ref.py makes it)"}
+    out = {"algorithmic_bytes_per_element": 2.5625, "shapes": []}
+    lib_path = os.path.join(ROOT, "baseline", "_ref", "libref_quantize_nvfp4.so")
+    ref_cuda = None
+    if os.path.exists(lib_path):
+        try:
+            L = ctypes.CDLL(lib_path)
+            vp, i64 = ctypes.c_void_p, ctypes.c_int64
+            L.launch_quantize_nvfp4_kernel.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, ctypes.c_float, ctypes.c_int,
+                                                       ctypes.c_bool, vp]
+            L.launch_quantize_nvfp4_kernel.restype = None
+
+            def ref_cuda(x, t):
+                # what the reference's host wrapper does per call (comfy_kitchen/backends/cuda/__init__.py:582-667):
+                # a zero-filled scale tensor (its kernel leaves the padding unwritten), then the launch
+                m, k = x.shape
+                q = torch.empty((m, k // 2), dtype=torch.uint8, device=x.device)
+                sf = torch.zeros(((m + 127) // 128 * 128, (k // 16 + 3) // 4 * 4), dtype=torch.uint8, device=x.device)
+                L.launch_quantize_nvfp4_kernel(x.data_ptr(), t.data_ptr(), q.data_ptr(), sf.data_ptr(), m, k, m, k, 0.0, 2,
+                                               True, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                return q, sf
+        except Exception as ex:
+            out["reference_cuda_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
+    triton_q = None
+    try:
+        from comfy_kitchen.backends.triton.quantization import quantize_nvfp4 as triton_q
+    except Exception as ex:
+        out["reference_triton_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
+    seen = set()
+    for name, x, t in zip(names, xs, ts_x):
+        if tuple(x.shape) in seen or x.shape[0] % 16:
+            continue
+        seen.add(tuple(x.shape))
+        nbytes = x.numel() * 2.5625
+        with ck.use_backend("eager"):
+            q_e, sf_e = ck.quantize_nvfp4(x, t.reshape(()))
+        sf_e = sf_e.view(torch.uint8)
+        entry = {"activation": name, "M": x.shape[0], "K": x.shape[1]}
+        impls = {"ours": lambda x=x, t=t: ckb.quantize_nvfp4(x, t)}
+        if ref_cuda is not None:
+            impls["reference_cuda"] = lambda x=x, t=t: ref_cuda(x, t.reshape(1))
+        if triton_q is not None:
+            impls["reference_triton"] = lambda x=x, t=t: triton_q(x, t.reshape(()))
+        for key, fn in impls.items():
+            try:
+                q, sf = fn()
+                torch.cuda.synchronize()
+                diff_q = int((q != q_e).sum())
+                diff_sf = int((sf.view(torch.uint8) != sf_e).sum())
+                replay, _ = B.graphed(fn)
+                ms = B.timed(replay, 20, all_ranks=False) / 20
+                entry[key] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "packed_bytes_differing_from_eager": diff_q,
+                              "scale_bytes_differing_from_eager": diff_sf, "of_packed_bytes": q.numel()}
+            except Exception as ex:
+                entry[key] = {"unavailable": f"{type(ex).__name__}: {ex}"[:200]}
+            B.graphs.clear()
+        out["shapes"].append(entry)
+    return out
+
+
+def fp4_ceiling(B: Bench):
+    """cuBLASLt's NVFP4 kernel (through torch) on 8192^3 and 16384^3, the measured ceiling for a block-scaled FP4 GEMM on
+    this GPU: best of 10 single launches (burst) and back to back for about two seconds (sustained), with this
+    library's kernel on the same operands beside it."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    out = {"how": "torch.nn.functional.scaled_mm (cuBLASLt NVFP4) and ck_b200_scaled_mm_nvfp4 on the same quantized "
+                  "N(0,1) operands; burst = best of 10 launches, sustained = back to back for ~2 s", "shapes": []}
+    best = 0.0
+    for n in (8192, 16384):
+        g = torch.Generator(device=B.dev).manual_seed(n)
+        a = torch.randn((n, n), generator=g, device=B.dev, dtype=torch.bfloat16)
+        b = torch.randn((n, n), generator=g, device=B.dev, dtype=torch.bfloat16)
+        ta, tb = ckb.dynamic_scale_nvfp4(a), ckb.dynamic_scale_nvfp4(b)
+        qa, sfa = ckb.quantize_nvfp4(a, ta)
+        qb, sfb = ckb.quantize_nvfp4(b, tb)
+        del a, b
+        fl = 2.0 * n * n * n
+        entry = {"M": n, "N": n, "K": n}
+        impls = {"ours": lambda: ckb.scaled_mm_nvfp4(qa, qb, ta, tb, sfa, sfb)}
+        try:
+            cublaslt_nvfp4(torch, qa, sfa, ta, qb, sfb, tb)
+            impls["cublaslt"] = lambda: cublaslt_nvfp4(torch, qa, sfa, ta, qb, sfb, tb)
+        except Exception as ex:   # depends on the torch / cuBLASLt build
+            entry["cublaslt_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
+        for key, fn in impls.items():
+            replay, _ = B.graphed(fn)
+            for _ in range(3):
+                replay()
+            burst = min(B.timed(replay, 1, all_ranks=False) for _ in range(10))
+            sampler = ClockSampler(B.local_rank).start()
+            ms, reps = B.for_seconds(replay, 2.0, 20)
+            clocks = sampler.stop()
+            entry[key] = {"burst_tflops": fl / (burst * 1e-3) / 1e12, "sustained_tflops": fl * reps / (ms * 1e-3) / 1e12,
+                          "sustained_sm_mhz_median": clocks.get("sm_mhz"), "sustained_power_w_median": clocks.get("power_w_median"),
+                          "sustained_reasons": clocks.get("reasons")}
+            if key == "cublaslt":
+                best = max(best, entry[key]["burst_tflops"])
+            B.graphs.clear()
+        out["shapes"].append(entry)
+        del qa, qb, sfa, sfb
+        torch.cuda.empty_cache()
+    out["best_cublaslt_burst_tflops"] = best if best > 0 else None
+    return out
+
+
+def quantize_sweep(B: Bench):
+    """quantize_nvfp4 / dequantize_nvfp4 on the twelve shapes of the bandwidth-sweep configuration, 2.5625 algorithmic
+    bytes per element.  L2-warm: one input replayed (inputs up to ~100 MB then stay in the 126 MB L2).  L2-cold: a
+    captured sequence over enough different inputs and outputs to exceed 4x the L2, so every launch reads HBM; for
+    inputs above 0.5 GB one buffer is cold by itself."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    sweep = []
+    for (sm, sk) in SWEEP_SHAPES:
+        in_bytes = sm * sk * 2
+        nbuf = 1 if in_bytes > (512 << 20) else max(2, -(-(4 * L2_BYTES) // in_bytes))
+        nbuf = min(nbuf, 96)
+        gx = torch.Generator(device=B.dev).manual_seed(sm + sk)
+        bufs = [torch.randn((sm, sk), generator=gx, device=B.dev, dtype=torch.bfloat16) for _ in range(nbuf)]
+        tt = ckb.dynamic_scale_nvfp4(bufs[0])
+        quant = [ckb.quantize_nvfp4(x, tt) for x in bufs]
+        nbytes = sm * sk * 2.5625
+        entry = {"M": sm, "K": sk, "input_mb": in_bytes / 1e6, "cold_buffers": nbuf}
+
+        def q_all():
+            return [ckb.quantize_nvfp4(x, tt) for x in bufs]
+
+        def d_all():
+            return [ckb.dequantize_nvfp4(q, tt, s, torch.bfloat16) for q, s in quant]
+
+        for key, fn_all, fn_one in (("quantize", q_all, lambda: ckb.quantize_nvfp4(bufs[0], tt)),
+                                    ("dequantize", d_all, lambda: ckb.dequantize_nvfp4(quant[0][0], tt, quant[0][1], torch.bfloat16))):
+            reps = 5 if nbuf > 1 else 10
+            r_cold, _ = B.graphed(fn_all)
+            t_cold = B.timed(r_cold, reps, all_ranks=False) / (reps * nbuf)
+            entry[f"{key}_cold_us"] = t_cold * 1e3
+            entry[f"{key}_cold_gbs"] = nbytes / (t_cold * 1e-3) / 1e9
+            B.graphs.clear()
+            if nbuf > 1:
+                r_warm, _ = B.graphed(fn_one)
+                t_warm = B.timed(r_warm, 20, all_ranks=False) / 20
+                entry[f"{key}_warm_us"] = t_warm * 1e3
+                entry[f"{key}_warm_gbs"] = nbytes / (t_warm * 1e-3) / 1e9
+                B.graphs.clear()
+        sweep.append(entry)
+        del bufs, quant
+        torch.cuda.empty_cache()
+    return sweep
+
+
+def small_m_sweep(B: Bench):
+    """T5-XXL-style feed-forward shapes (d = 4096, ff = 10240): latency of one linear (quantize + GEMM, split-K below
+    129 rows) per M."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    small_m = []
+    gsm = torch.Generator(device=B.dev).manual_seed(5)
+    for (sk, sn) in [(4096, 10240), (10240, 4096)]:
+        ww = torch.randn((sn, sk), generator=gsm, device=B.dev, dtype=torch.bfloat16) * 0.02
+        wts = ckb.dynamic_scale_nvfp4(ww)
+        wq, wsf = ckb.quantize_nvfp4(ww, wts)
+        for sm in (1, 16, 64, 512):
+            xx = torch.randn((sm, sk), generator=gsm, device=B.dev, dtype=torch.bfloat16)
+            tt = ckb.dynamic_scale_nvfp4(xx)
+            qq, ss = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
+
+            def lin_call(xx=xx, tt=tt, wq=wq, wts=wts, wsf=wsf):
+                q1, s1 = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
+                return ckb.scaled_mm_nvfp4(q1, wq, tt, wts, s1, wsf)
+            r_l, _ = B.graphed(lin_call)
+            r_g, n_g = B.graphed(lambda: ckb.scaled_mm_nvfp4(qq, wq, tt, wts, ss, wsf))
+            reps = 50
+            t_l = B.timed(r_l, reps, all_ranks=False) / reps
+            t_g = B.timed(r_g, reps, all_ranks=False) / reps
+            small_m.append({"M": sm, "K": sk, "N": sn, "linear_us": t_l * 1e3, "gemm_us": t_g * 1e3,
+                            "gemm_kernels": n_g, "gemm_tflops": 2.0 * sm * sn * sk / (t_g * 1e-3) / 1e12,
+                            "weight_gbs": sn * sk * 0.5625 / (t_g * 1e-3) / 1e9})
+            del r_l, r_g
+            B.graphs.clear()
+        del ww, wq, wsf
+    torch.cuda.empty_cache()
+    return small_m
+
+
+def mxfp8_record(B: Bench, wl, xs, ws_cpu, steps):
+    """The MXFP8 sibling path on the same workload: quantizer GB/s (3.03125 algorithmic bytes per element: 2 in, 1 out,
+    1/32 scale) and GEMM TFLOP/s per linear, with cuBLASLt's MXFP8 kernel beside it."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    M = wl["M"]
+    mx_lin, mq_ms, mg_ms, mc_ms, m_fl, m_bytes = [], 0.0, 0.0, 0.0, 0.0, 0.0
+    for i, (name, k, n) in enumerate(wl["linears"]):
+        wq8, wsf8 = ckb.quantize_mxfp8(ws_cpu[i].to(B.dev), pad_32x=True)
+        xq8, xsf8 = ckb.quantize_mxfp8(xs[i], pad_32x=True)
+        rq8, _ = B.graphed(lambda i=i: ckb.quantize_mxfp8(xs[i], pad_32x=True))
+        rg8, _ = B.graphed(lambda xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8: ckb.scaled_mm_mxfp8(xq8, wq8, xsf8, wsf8))
+        tq8 = B.timed(rq8, steps, all_ranks=False) / steps
+        tg8 = B.timed(rg8, steps, all_ranks=False) / steps
+        entry = {"linear": name, "quantize_us": tq8 * 1e3, "quantize_gbs": M * k * 3.03125 / (tq8 * 1e-3) / 1e9,
+                 "gemm_us": tg8 * 1e3, "gemm_tflops": 2.0 * M * n * k / (tg8 * 1e-3) / 1e12}
+        try:
+            from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
+
+            def lt(xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8):
+                return scaled_mm(xq8, wq8.t(), scale_a=xsf8.view(-1), scale_b=wsf8.view(-1),
+                                 scale_recipe_a=ScalingType.BlockWise1x32, scale_recipe_b=ScalingType.BlockWise1x32,
+                                 swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4,
+                                 output_dtype=torch.bfloat16)
+            rc8, _ = B.graphed(lt)
+            tc8 = B.timed(rc8, steps, all_ranks=False) / steps
+            entry["cublaslt_gemm_tflops"] = 2.0 * M * n * k / (tc8 * 1e-3) / 1e12
+            mc_ms += tc8
+        except Exception as ex:   # depends on the torch / cuBLASLt build
+            entry["cublaslt_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
+        mx_lin.append(entry)
+        mq_ms += tq8
+        mg_ms += tg8
+        m_fl += 2.0 * M * n * k
+        m_bytes += M * k * 3.03125
+        del wq8, wsf8, xq8, xsf8
+        B.graphs.clear()
+    torch.cuda.empty_cache()
+    return {"gemm_tflops": m_fl / (mg_ms * 1e-3) / 1e12, "quantize_gbs": m_bytes / (mq_ms * 1e-3) / 1e9,
+            "cublaslt_gemm_tflops": (m_fl / (mc_ms * 1e-3) / 1e12) if mc_ms > 0 else None,
+            "nominal_dense_fp8_tflops": 4500.0, "per_linear": mx_lin,
+            "kernel": "gemm_nvfp4_pair_kernel<KB, DBG, FMT = 1> (CTA pairs, tcgen05 kind::mxf8f6f4.block_scale)"}
+
+
+def wan_record(B: Bench, args):
+    """A short record (5 steps) of the Wan-class workload (M = 32760, hidden 5120, FFN 13824), the configuration whose
+    weights are N-sharded over the GPUs: step time and TFLOP/s at this GPU count, the collective used, and the check
+    of the fused result against the NCCL all-gather."""
+    torch = B.torch
+    wl = WAN
+    xs, ws = make_inputs_on_device(wl, B.dev, torch.bfloat16)
+    plan = StepPlan(B, wl, xs, ws, args.collective)
+    del ws
+    torch.cuda.empty_cache()
+    steps = 5
+    try:
+        for _ in range(3):
+            plan.step()
+        B.barrier()
+        parity = plan.check_parity() if B.distributed else None
+        replay, launches = B.graphed(plan.step, use_graph=plan.use_graph)
+        for _ in range(2):
+            replay()
+        ms = B.timed(replay, steps) / steps
+        fl = flops_per_step(wl)
+        rec = {"workload": wl["name"], "M": wl["M"], "linears": [list(l) for l in wl["linears"]], "steps": steps,
+               "ms_per_step": ms, "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": B.world,
+               "mode": plan.mode_text(), "launch": "one CUDA graph per step" if plan.use_graph else "eager launches",
+               "gpu_launches_per_step": launches, "parity": parity,
+               "data": "synthetic, generated on the device from a seeded generator"}
+        if plan.fused:
+            out_bytes = sum(wl["M"] * lin.local_rows * 2 for lin in plan.layers) * (B.world - 1)
+            rec["nvlink_achieved_gbs"] = out_bytes / (ms * 1e-3) / 1e9
+        if B.distributed:
+            ingress = (B.world - 1) / B.world * sum(wl["M"] * n * 2 for _, _, n in wl["linears"])
+            rec["ingress_bound_ms_at_770_gbs"] = ingress / 770e9 * 1e3
+        return rec
+    finally:
+        B.graphs.clear()
+        plan.close()
+        del plan, xs
+        torch.cuda.empty_cache()
+
+
 def run_ours(args, wl):
     import torch
-    import torch.distributed as dist
+
     import comfy_kitchen_b200 as ckb
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: comfy_kitchen_b200 has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    B = Bench(args)
+    dist, dev, rank, world, distributed = B.dist, B.dev, B.rank, B.world, B.distributed
     if args.no_dependent_launch:
         ckb.set_tuning(3, 0)
     elif args.dependent_launch_mask is not None:
         ckb.set_tuning(3, args.dependent_launch_mask)
-    distributed = world > 1
-    if distributed:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    # N > 1, default: the GEMM's epilogue stores its tiles into every rank's output matrix (peer memory over
-    # NVLink) and the ranks meet at a stream-ordered barrier kernel before and after the step, so a step holds no
-    # library collective and is captured in a CUDA graph like the single-GPU step.  --collective nccl keeps the
-    # NCCL all-gather instead; it launches eagerly: a captured step with all-gathers in it ran 5 % faster on 2 GPUs
-    # but the process then hung while tearing the process group down, so library collectives stay out of graphs
-    fused = distributed and args.collective == "fused"
-    use_graph = (not distributed or fused) and not args.no_graph
-    # --fused-linear: each linear is one call of the library's whole-linear entry point with the quantizer inside
-    # the GEMM kernel (same bits as quantize_nvfp4 followed by scaled_mm_nvfp4; measured slower, so not the default)
     one_call = args.fused_linear
     if one_call:
         ckb.set_tuning(4, 1)
 
     M = wl["M"]
     pad_m = M % 16 != 0
-    xs_cpu, ws_cpu = make_inputs(wl, "cpu", torch.bfloat16)
+    xs_cpu, ws_cpu = make_inputs(wl, torch.bfloat16)
     xs = [x.to(dev) for x in xs_cpu]
-    # static per-tensor activation scales (the optional `input_scale` of an NVFP4 checkpoint), amax/(448*6)
-    ts_x = [ckb.dynamic_scale_nvfp4(x) for x in xs]
-    layers = [ckb.ShardedNVFP4Linear(w.to(dev), None, input_scale=t) for w, t in zip(ws_cpu, ts_x)]
-    torch.cuda.synchronize()
-    side = torch.cuda.Stream()
-    graphs = []
+    plan = StepPlan(B, wl, xs, ws_cpu, args.collective)
+    layers, ts_x, fused = plan.layers, plan.ts_x, plan.fused
 
-    equal_shards = all(n % (8 * world) == 0 for _, _, n in wl["linears"])
-    peers = None
-    if fused and not (equal_shards and M > 128 and all(n // world > 128 for _, _, n in wl["linears"])):
-        fused = False            # the fused kernel wants equal shards wider than 128 columns and more than 128 rows
-        use_graph = False
-    # The fused path maps every rank's output matrices into every process.  With 18 GB of peer mappings (the Wan
-    # workload on 8 GPUs: 7 peers x 2.6 GB) its stores ran at 96 GB/s per rank, 23.4 ms per step, where the NCCL
-    # all-gather, which stages through small buffers, took 4.1 ms; with 1.8 GB (Flux, 8 GPUs) and 2.6 GB (Wan, 2 GPUs)
-    # the fused path ran at 420-480 GB/s.  Large footprints therefore take the NCCL path.
-    peer_bytes = (world - 1) * sum(M * n * 2 for _, _, n in wl["linears"])
-    fused_declined = None
-    if fused and peer_bytes > (4 << 30):
-        fused = False
-        use_graph = False
-        fused_declined = f"{peer_bytes / 2**30:.1f} GiB of peer-mapped output matrices per rank: NCCL all-gather instead"
-    if fused:
-        peers = ckb.PeerGroup(dev)
-        for lin in layers:
-            lin.bind(peers, M)
-
-    def step(one_call=one_call):
-        # the linears of a step are independent work items: the all-gather of one overlaps the quantizer and GEMM
-        # of the next (the collective runs on the process group's stream); all of them are awaited before the
-        # step ends
-        if fused:
-            peers.barrier()                       # every rank is done with the previous step's matrices
-            outs = [lin.fused(x) for x, lin in zip(xs, layers)]
-            peers.barrier()                       # every rank's column blocks have arrived
-            return outs
-        outs, pending = [], []
-        for x, lin in zip(xs, layers):
-            y = lin.local(x, one_call=one_call)
-            if not distributed:
-                outs.append(y)
-            elif equal_shards:
-                work, buf = lin.gather_async(y)
-                pending.append(work)
-                outs.append(buf)
-            else:
-                outs.append(lin.gather(y, row_major=False))
-        for work in pending:
-            work.wait()
-        return outs
-
-    def barrier():
-        if distributed:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def graphed(fn):
-        """Capture fn once (after warm-up on the capture stream) and return (replay, launches per replay)."""
-        if not use_graph:
-            n0 = ckb.launches()
-            fn()
-            return fn, ckb.launches() - n0
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                fn()
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        n0 = ckb.launches()
-        with torch.cuda.graph(g, stream=side):
-            keep = fn()
-        n = ckb.launches() - n0
-        g._keep = keep
-        graphs.append(g)
-        return g.replay, n
-
-    def timed(replay, reps):
-        """reps back-to-back replays between two CUDA events on the current stream; returns ms in total."""
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        a.record()
-        for _ in range(reps):
-            replay()
-        b.record()
-        barrier()
-        ms = a.elapsed_time(b)
-        if distributed:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(B.local_rank)
     if rank == 0:
         sampler.start()
 
     warm = max(3, args.warmup)
     for _ in range(warm):
-        step()
-    barrier()
+        plan.step(one_call=one_call)
+    B.barrier()
     assert ckb.read_device_status() == 0, "a bounded wait ran out during warm-up"
 
+    # ---- parity of the path about to be timed, inside this run ----
+    parity = plan.check_parity()
+    if rank == 0 and not parity.get("ok", True):
+        print(json.dumps({"error": "parity check failed", "parity": parity}), flush=True)
+    if not parity.get("ok", True):
+        plan.close()
+        if distributed:
+            dist.destroy_process_group()
+        sys.exit(3)
+
     # ---- the timed region: exactly K steps ----
-    replay_step, launches_per_step = graphed(step)
+    replay_step, launches_per_step = B.graphed(lambda: plan.step(one_call=one_call), use_graph=plan.use_graph)
     for _ in range(warm):
         replay_step()
-    ms = timed(replay_step, args.steps)
+    ms = B.timed(replay_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}      # the samples cover warm-up and the timed region only
     launches = launches_per_step * args.steps
     fl = flops_per_step(wl)
     value = fl * args.steps / (ms * 1e-3) / 1e12
+
+    # ---- the same K steps with the quantizers on a second branch of the graph (independent linears overlap) ----
+    overlapped = None
+    if plan.use_graph and not one_call:
+        replay_o, n_o = B.graphed(plan.step_overlapped)
+        for _ in range(warm):
+            replay_o()
+        ms_o = B.timed(replay_o, args.steps)
+        overlapped = {"ms_per_step": ms_o / args.steps, "value": fl * args.steps / (ms_o * 1e-3) / 1e12,
+                      "gpu_launches_per_step": n_o,
+                      "what": "one CUDA graph with two branches: the quantizer of linear i+1 runs beside the GEMM "
+                              "of linear i (the step's linears are independent work items); `value` above is the "
+                              "serial chain"}
+        if fused:
+            out_bytes = sum(M * lin.local_rows * 2 for lin in layers) * (world - 1)
+            overlapped["nvlink_achieved_gbs"] = out_bytes / (ms_o / args.steps * 1e-3) / 1e9
+
+    # ---- the step with per-call (dynamic) activation scales: what the layer does when a checkpoint has no input_scale
+    dynamic = None
+    if not one_call:
+        replay_d, n_d = B.graphed(lambda: plan.step(dynamic=True), use_graph=plan.use_graph)
+        for _ in range(warm):
+            replay_d()
+        ms_d = B.timed(replay_d, args.steps)
+        dynamic = {"ms_per_step": ms_d / args.steps, "value": fl * args.steps / (ms_d * 1e-3) / 1e12,
+                   "gpu_launches_per_step": n_d, "slowdown_vs_static": ms_d / ms - 1.0,
+                   "what": "input_scale = None: amax(|x|)/(448*6) in the activation's dtype derived on the device in "
+                           "front of every quantizer (comfy_kitchen/tensor/nvfp4.py:66-71), no host round trip"}
+
+    # ---- sustained: the step graph replayed for seconds, with the clocks NVML shows meanwhile (single-GPU runs) ----
+    sustained = None
+    if not distributed and not args.no_sweep:
+        s2 = ClockSampler(B.local_rank).start()
+        ms_s, reps_s = B.for_seconds(replay_step, args.sustained_seconds, 200)
+        c2 = s2.stop()
+        v = fl * reps_s / (ms_s * 1e-3) / 1e12
+        sustained = {"seconds": ms_s / 1e3, "steps": reps_s, "ms_per_step": ms_s / reps_s, "value": v, "unit": "TFLOP/s",
+                     "sm_mhz_median": c2.get("sm_mhz"), "sm_mhz_min": c2.get("sm_min_mhz"), "sm_max_mhz": c2.get("sm_max_mhz"),
+                     "power_w_median": c2.get("power_w_median"), "power_w_max": c2.get("power_w_max"),
+                     "reasons": c2.get("reasons"),
+                     "value_scaled_to_max_clock": (v * c2["sm_max_mhz"] / c2["sm_mhz"]) if c2.get("sm_mhz") else None,
+                     "burst_over_sustained": value / v,
+                     "what": "the same CUDA graph as `value`, replayed back to back for this long; `value` itself is a "
+                             "burst figure (K steps, a few ms)"}
+
     fused_linear = None
     if not distributed and not one_call and not args.no_sweep:
         # the same step with the quantizer inside the GEMM kernel (one kernel per linear), for comparison
         ckb.set_tuning(4, 1)
-        replay_f, _ = graphed(lambda: step(one_call=True))
+        replay_f, _ = B.graphed(lambda: plan.step(one_call=True))
         for _ in range(warm):
             replay_f()
-        ms_f = timed(replay_f, args.steps)
+        ms_f = B.timed(replay_f, args.steps)
         ckb.set_tuning(4, 0)
         fused_linear = {"ms_per_step": ms_f / args.steps, "value": fl * args.steps / (ms_f * 1e-3) / 1e12,
                         "what": "ck_b200_linear_nvfp4 with the activation quantizer inside the GEMM kernel "
@@ -375,10 +922,10 @@ def run_ours(args, wl):
     per_linear = []
     gemm_ms = quant_ms = gemm_fl = quant_bytes = 0.0
     for i, ((name, k, n), lin) in enumerate(zip(wl["linears"], layers)):
-        rg, _ = graphed(one_gemm(i))
-        rq, _ = graphed(one_quant(i))
-        tg = timed(rg, args.steps) / args.steps
-        tq = timed(rq, args.steps) / args.steps
+        rg, _ = B.graphed(one_gemm(i))
+        rq, _ = B.graphed(one_quant(i))
+        tg = B.timed(rg, args.steps) / args.steps
+        tq = B.timed(rq, args.steps) / args.steps
         n_local = lin.local_rows
         per_linear.append({"linear": name, "K": k, "N_local": n_local, "quantize_us": tq * 1e3, "gemm_us": tg * 1e3,
                            "gemm_tflops": 2.0 * M * n_local * k / (tg * 1e-3) / 1e12,
@@ -395,147 +942,69 @@ def run_ours(args, wl):
         t_rows = 0.0
         for i in range(len(layers)):
             x_rows = xs[i][r0:r1]
-            rs, _ = graphed(lambda x_rows=x_rows, i=i: ckb.quantize_nvfp4(x_rows, ts_x[i], pad_16x=True))
-            t_rows += timed(rs, args.steps) / args.steps
+            rs, _ = B.graphed(lambda x_rows=x_rows, i=i: ckb.quantize_nvfp4(x_rows, ts_x[i], pad_16x=True))
+            t_rows += B.timed(rs, args.steps) / args.steps
         row_sharded = {"aggregate_gbs": quant_bytes / (t_rows * 1e-3) / 1e9, "rows_per_rank": r1 - r0,
                        "us_per_step": t_rows * 1e3, "note": "weak in bytes per rank / strong in total: M rows split over the ranks"}
+    B.graphs.clear()
     peaks = measured_peaks()
     gemm_tflops = gemm_fl / (gemm_ms * 1e-3) / 1e12
     quant_gbs = quant_bytes / (quant_ms * 1e-3) / 1e9
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
+
+    # ---- cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend ----
+    try:
+        tot, per = 0.0, {}
+        for i in range(len(layers)):
+            (q, sf), t, (w_q, w_sf, w_ts) = qx_all[i], ts_x[i], qw[i]
+            rc, _ = B.graphed(lambda q=q, sf=sf, t=t, w_q=w_q, w_sf=w_sf, w_ts=w_ts: cublaslt_nvfp4(torch, q, sf, t, w_q, w_sf, w_ts))
+            tc = B.timed(rc, args.steps) / args.steps
+            tot += tc
+            per[wl["linears"][i][0]] = 2.0 * M * layers[i].local_rows * wl["linears"][i][1] / (tc * 1e-3) / 1e12
+        cublaslt = {"gemm_tflops": gemm_fl / (tot * 1e-3) / 1e12, "per_linear_tflops": per,
+                    "ours_over_cublaslt": {pl["linear"]: pl["gemm_tflops"] / per[pl["linear"]] for pl in per_linear},
+                    "what": "torch.nn.functional.scaled_mm (cuBLASLt NVFP4), same operands, GEMM only, timed like ours"}
+    except Exception as ex:   # depends on the torch / cuBLASLt build
+        cublaslt = {"unavailable": f"{type(ex).__name__}: {ex}"[:200]}
+    B.graphs.clear()
+
+    # ---- the measured ceiling for a block-scaled FP4 GEMM on this GPU (single-GPU runs) ----
+    ceiling = None
+    if not distributed and not args.no_sweep:
+        ceiling = fp4_ceiling(B)
+    ceiling_peak = (ceiling or {}).get("best_cublaslt_burst_tflops")
+
     roofline = {
-        "kernel": "gemm_nvfp4_kernel", "bound": "tensor", "achieved": gemm_tflops, "peak": NOMINAL_NVFP4_TFLOPS,
+        "kernel": "gemm_nvfp4_pair_kernel<128, false, 0, -1> (CTA pairs, 256x256 tiles, tcgen05 cta_group::2)",
+        "bound": "tensor", "achieved": gemm_tflops, "peak": NOMINAL_NVFP4_TFLOPS,
         "unit": "TFLOP/s", "frac": gemm_tflops / NOMINAL_NVFP4_TFLOPS,
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch (mean of the four Flux launches) from the ncu capture
-        # summarised in profiles/gemm_nvfp4_pair_kernel_flux.md; other workloads / shard sizes were not captured
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of the four Flux launches
         "traffic": 56.45e6 if (args.workload == "flux" and world == 1) else None,
+        "traffic_source": "one ncu capture of these four launches (summary under profiles/), not measured in this run",
         "peak_source": "nominal dense NVFP4 (vendor figure); MEASURED_PEAKS.json has no FP4 entry",
+        "peak_measured_cublaslt": ceiling_peak,
+        "frac_of_measured_cublaslt": (gemm_tflops / ceiling_peak) if ceiling_peak else None,
         "frac_of_4x_measured_bf16": (gemm_tflops / (4.0 * peaks["bf16_tflops"])) if "bf16_tflops" in peaks else None,
         "algorithmic_flops_per_launch": gemm_fl / len(layers), "avg_launch_us": gemm_ms * 1e3 / len(layers),
         "timing": "each linear's kernel replayed back to back K times between CUDA events (same-input repeats: operands "
                   "stay in L2, as they do inside a step where the quantizer has just written them)",
-        "quantize": {"kernel": "quantize_nvfp4_flat_kernel (inputs of 20 MB to 0.25 GB) / quantize_nvfp4_kernel", "bound": "hbm", "achieved": quant_gbs, "peak": hbm_peak,
+        "quantize": {"kernel": "quantize_nvfp4_flat_kernel<bf16, vec, 2> (inputs of 20 MB to 0.25 GB; "
+                               "quantize_nvfp4_kernel outside that range)",
+                     "bound": "hbm", "achieved": quant_gbs, "peak": hbm_peak,
                      "unit": "GB/s", "frac": quant_gbs / hbm_peak,
                      "peak_source": "measured copy (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks else "fallback",
                      "frac_of_nominal_8000": quant_gbs / 8000.0, "algorithmic_bytes_per_element": 2.5625,
-                     "note": "activations of 28-113 MB: repeats of one input are partly L2 resident"},
+                     "note": "activations of 28-113 MB: repeats of one input are partly L2 resident; the sweep gives "
+                             "L2-cold and L2-warm figures per shape"},
         "per_linear": per_linear,
     }
 
-    # ---- bandwidth sweep of the quantizer / dequantizer (shapes of the M x K bandwidth-sweep configuration), single-GPU runs only:
-    # timed() synchronises all ranks, so every rank would have to run it ----
-    sweep = None
+    sweep = small_m = mxfp8 = comparators = None
     if not distributed and not args.no_sweep:
-        sweep = []
-        for (sm, sk) in [(1024, 3072), (4096, 5120), (16384, 3072), (16384, 12288), (65536, 5120), (65536, 12288)]:
-            gx = torch.Generator(device=dev).manual_seed(sm + sk)
-            xx = torch.randn((sm, sk), generator=gx, device=dev, dtype=torch.bfloat16)
-            tt = ckb.dynamic_scale_nvfp4(xx)
-            qq, ss = ckb.quantize_nvfp4(xx, tt)
-            reps = 10
-            r_q, _ = graphed(lambda: ckb.quantize_nvfp4(xx, tt))
-            r_d, _ = graphed(lambda: ckb.dequantize_nvfp4(qq, tt, ss, torch.bfloat16))
-            t_q = timed(r_q, reps) / reps
-            t_d = timed(r_d, reps) / reps
-            nbytes = sm * sk * 2.5625
-            sweep.append({"M": sm, "K": sk, "quantize_us": t_q * 1e3, "quantize_gbs": nbytes / (t_q * 1e-3) / 1e9,
-                          "dequantize_us": t_d * 1e3, "dequantize_gbs": nbytes / (t_d * 1e-3) / 1e9})
-            del xx, qq, ss, r_q, r_d
-            graphs.clear()
-        torch.cuda.empty_cache()
-
-    # ---- small-M sweep (T5-XXL-style feed-forward shapes, d = 4096, ff = 10240), single-GPU runs:
-    # latency of one linear (quantize + GEMM, split-K below 129 rows) per M ----
-    small_m = None
-    if not distributed and not args.no_sweep:
-        small_m = []
-        gsm = torch.Generator(device=dev).manual_seed(5)
-        for (sk, sn) in [(4096, 10240), (10240, 4096)]:
-            ww = torch.randn((sn, sk), generator=gsm, device=dev, dtype=torch.bfloat16) * 0.02
-            wts = ckb.dynamic_scale_nvfp4(ww)
-            wq, wsf = ckb.quantize_nvfp4(ww, wts)
-            for sm in (1, 16, 64, 512):
-                xx = torch.randn((sm, sk), generator=gsm, device=dev, dtype=torch.bfloat16)
-                tt = ckb.dynamic_scale_nvfp4(xx)
-                qq, ss = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
-                def lin_call(xx=xx, tt=tt, wq=wq, wts=wts, wsf=wsf):
-                    q1, s1 = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
-                    return ckb.scaled_mm_nvfp4(q1, wq, tt, wts, s1, wsf)
-                r_l, _ = graphed(lin_call)
-                r_g, _ = graphed(lambda: ckb.scaled_mm_nvfp4(qq, wq, tt, wts, ss, wsf))
-                reps = 50
-                t_l = timed(r_l, reps) / reps
-                t_g = timed(r_g, reps) / reps
-                small_m.append({"M": sm, "K": sk, "N": sn, "linear_us": t_l * 1e3, "gemm_us": t_g * 1e3,
-                                "gemm_tflops": 2.0 * sm * sn * sk / (t_g * 1e-3) / 1e12,
-                                "weight_gbs": sn * sk * 0.5625 / (t_g * 1e-3) / 1e9})
-                del r_l, r_g
-                graphs.clear()
-            del ww, wq, wsf
-        torch.cuda.empty_cache()
-
-    # ---- the MXFP8 sibling path on the same workload (single-GPU runs): quantizer GB/s (3.03125 algorithmic bytes per
-    # element: 2 in, 1 out, 1/32 scale) and GEMM TFLOP/s per linear, with cuBLASLt's MXFP8 kernel beside it ----
-    mxfp8 = None
-    if not distributed and not args.no_sweep:
-        mx_lin, mq_ms, mg_ms, mc_ms, m_fl, m_bytes = [], 0.0, 0.0, 0.0, 0.0, 0.0
-        for i, (name, k, n) in enumerate(wl["linears"]):
-            wq8, wsf8 = ckb.quantize_mxfp8(ws_cpu[i].to(dev), pad_32x=True)
-            xq8, xsf8 = ckb.quantize_mxfp8(xs[i], pad_32x=True)
-            rq8, _ = graphed(lambda i=i: ckb.quantize_mxfp8(xs[i], pad_32x=True))
-            rg8, _ = graphed(lambda xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8: ckb.scaled_mm_mxfp8(xq8, wq8, xsf8, wsf8))
-            tq8 = timed(rq8, args.steps) / args.steps
-            tg8 = timed(rg8, args.steps) / args.steps
-            entry = {"linear": name, "quantize_us": tq8 * 1e3, "quantize_gbs": M * k * 3.03125 / (tq8 * 1e-3) / 1e9,
-                     "gemm_us": tg8 * 1e3, "gemm_tflops": 2.0 * M * n * k / (tg8 * 1e-3) / 1e12}
-            try:
-                from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
-
-                def lt(xq8=xq8, wq8=wq8, xsf8=xsf8, wsf8=wsf8):
-                    return scaled_mm(xq8, wq8.t(), scale_a=xsf8.view(-1), scale_b=wsf8.view(-1),
-                                     scale_recipe_a=ScalingType.BlockWise1x32, scale_recipe_b=ScalingType.BlockWise1x32,
-                                     swizzle_a=SwizzleType.SWIZZLE_32_4_4, swizzle_b=SwizzleType.SWIZZLE_32_4_4,
-                                     output_dtype=torch.bfloat16)
-                rc8, _ = graphed(lt)
-                tc8 = timed(rc8, args.steps) / args.steps
-                entry["cublaslt_gemm_tflops"] = 2.0 * M * n * k / (tc8 * 1e-3) / 1e12
-                mc_ms += tc8
-            except Exception as ex:   # depends on the torch / cuBLASLt build
-                entry["cublaslt_unavailable"] = f"{type(ex).__name__}: {ex}"[:160]
-            mx_lin.append(entry)
-            mq_ms += tq8
-            mg_ms += tg8
-            m_fl += 2.0 * M * n * k
-            m_bytes += M * k * 3.03125
-            del wq8, wsf8, xq8, xsf8
-            graphs.clear()
-        mxfp8 = {"gemm_tflops": m_fl / (mg_ms * 1e-3) / 1e12, "quantize_gbs": m_bytes / (mq_ms * 1e-3) / 1e9,
-                 "cublaslt_gemm_tflops": (m_fl / (mc_ms * 1e-3) / 1e12) if mc_ms > 0 else None,
-                 "nominal_dense_fp8_tflops": 4500.0, "per_linear": mx_lin,
-                 "kernel": "gemm_nvfp4_kernel<BN, FMT = 1> (1-CTA tiles, tcgen05 kind::mxf8f6f4.block_scale)"}
-        torch.cuda.empty_cache()
-
-    # ---- cuBLASLt NVFP4 through torch on the same operands: the kernel behind the reference eager backend ----
-    try:
-        from torch.nn.functional import ScalingType, SwizzleType, scaled_mm
-        tot = 0.0
-        for i in range(len(layers)):
-            (q, sf), t, (w_q, w_sf, w_ts) = qx_all[i], ts_x[i], qw[i]
-
-            def call(q=q, sf=sf, t=t, w_q=w_q, w_sf=w_sf, w_ts=w_ts):
-                return scaled_mm(q.view(torch.float4_e2m1fn_x2), w_q.view(torch.float4_e2m1fn_x2).t(),
-                                 scale_a=[sf.view(-1), t.reshape(())], scale_b=[w_sf.view(-1), w_ts.reshape(())],
-                                 scale_recipe_a=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
-                                 scale_recipe_b=[ScalingType.BlockWise1x16, ScalingType.TensorWise],
-                                 swizzle_a=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
-                                 swizzle_b=[SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE],
-                                 output_dtype=torch.bfloat16)
-            rc, _ = graphed(call)
-            tot += timed(rc, args.steps) / args.steps
-        cublaslt = {"gemm_tflops": gemm_fl / (tot * 1e-3) / 1e12,
-                    "what": "torch.nn.functional.scaled_mm (cuBLASLt NVFP4), same operands, GEMM only, timed like ours"}
-    except Exception as ex:   # depends on the torch / cuBLASLt build
-        cublaslt = {"unavailable": f"{type(ex).__name__}: {ex}"[:200]}
+        sweep = quantize_sweep(B)
+        small_m = small_m_sweep(B)
+        mxfp8 = mxfp8_record(B, wl, xs, ws_cpu, args.steps)
+        comparators = quantize_comparators(B, xs, ts_x, [l[0] for l in wl["linears"]])
 
     # ---- end to end: pinned host activations in, host outputs back, copies inside the timed region ----
     x_host = [x.pin_memory() for x in xs_cpu]
@@ -553,6 +1022,7 @@ def run_ours(args, wl):
     ev_cmp = [torch.cuda.Event() for _ in layers]
     ev_out = [torch.cuda.Event() for _ in layers]
     serial = args.e2e_serial
+    peers = plan.peers
 
     def e2e_step():
         cur = torch.cuda.current_stream()
@@ -586,7 +1056,7 @@ def run_ours(args, wl):
 
     for _ in range(2):
         e2e_step()
-    ems = timed(e2e_step, args.steps)
+    ems = B.timed(e2e_step, args.steps)
     e2e = {"value": fl * args.steps / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
            "pcie_gbs": {"h2d": h2d / (ems / args.steps * 1e-3) / 1e9, "d2h": d2h / (ems / args.steps * 1e-3) / 1e9},
@@ -603,13 +1073,38 @@ def run_ours(args, wl):
             torch.cuda.synchronize()
         ckb.set_tuning(2, 0)
     status = ckb.read_device_status()
-    clocks = sampler.stop() if rank == 0 else {}
+
+    nvlink = None
+    if fused:
+        # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate
+        out_bytes = sum(M * lin.local_rows * 2 for lin in layers) * (world - 1)
+        ingress = (world - 1) / world * sum(M * n * 2 for _, _, n in wl["linears"])
+        nvlink = {"bytes_out_per_rank_per_step": out_bytes,
+                  "achieved_gbs": out_bytes / (ms / args.steps * 1e-3) / 1e9, "peak_gbs": 770.0,
+                  "peak_source": "measured peer copy per direction on this pool",
+                  "ingress_bound_ms": ingress / 770e9 * 1e3,
+                  "note": "whole step in the denominator, quantizer kernels (no traffic) included"}
+
+    # release the Flux plan's peer memory before the Wan record maps its own
+    del qx_all, qw, x_dev, x_host, y_host, replay_step
+    B.graphs.clear()
+    plan.close()
+    torch.cuda.empty_cache()
+
+    # ---- the Wan-class workload, briefly, at this GPU count ----
+    wan = None
+    if not args.no_wan and args.workload == "flux":
+        try:
+            wan = wan_record(B, args)
+        except Exception as ex:
+            wan = {"failed": f"{type(ex).__name__}: {ex}"[:300]}
+        status = status or ckb.read_device_status()
 
     # ---- CPU baseline on a bounded sample (rank 0, single-GPU run only) ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         xs_bits, w_q, threads = prepare_cpu(wl, xs_cpu, ws_cpu)
-        rows = min(1152, M)
+        rows = min(CPU_SAMPLE_ROWS, M)
         cpu_reference_step(wl, xs_bits, w_q, rows)
         t0 = time.perf_counter()
         reps, cfl = 0, 0.0
@@ -618,39 +1113,28 @@ def run_ours(args, wl):
             reps += 1
         dt = time.perf_counter() - t0
         cpu = {"value": cfl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-               "sample": f"first {rows} of {M} tokens of each linear, {reps} repetitions, {dt:.1f} s of CPU work"}
+               "sample": f"{cpu_sample_text(wl, rows)}, {reps} repetitions, {dt:.1f} s of CPU work"}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x e4m3 block scales), fp32 accumulate",
-            "data": "synthetic",
-            "config": {"workload": wl["name"], "M": M, "linears": wl["linears"],
-                       "parallelism": f"weights N-sharded over {world} GPU(s)" + ((", all-gather of bf16 outputs fused into the GEMM epilogue (stores to peer memory over NVLink), "
-                                         "barrier kernel before and after the step") if fused else
-                                        ", NCCL all-gather of bf16 outputs (overlapping the next linear)"
-                                        + (f" [{fused_declined}]" if fused_declined else "") if distributed else ""),
-                       "launch": "one CUDA graph per step" if use_graph else "eager launches",
-                       "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
-                                  "(ck_b200_linear_nvfp4)") if one_call and not distributed else
-                                 "quantize_nvfp4 kernel, then scaled_mm_nvfp4 kernel",
-                       "l2": "no flush: one step touches ~0.6 GB (activations, packed operands, outputs), 5x the 126 MB L2"},
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": workload_config(wl),
+            "run": {"parallelism": plan.mode_text(),
+                    "launch": "one CUDA graph per step" if plan.use_graph else "eager launches",
+                    "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
+                               "(ck_b200_linear_nvfp4)") if one_call and not distributed else
+                              "quantize_nvfp4 kernel, then scaled_mm_nvfp4 kernel, the four linears one after the other"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "cublaslt_comparator": cublaslt, "device_status": status,
+            "parity": parity, "sustained": sustained, "overlapped": overlapped, "dynamic_scale_step": dynamic,
+            "fp4_ceiling": ceiling, "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
-            "quantize_sweep": sweep, "small_m_sweep": small_m, "mxfp8": mxfp8, "fused_linear": fused_linear,
+            "quantize_sweep": sweep, "quantize_comparators": comparators, "small_m_sweep": small_m, "mxfp8": mxfp8,
+            "fused_linear": fused_linear, "wan": wan,
         }
-        if fused:
-            # bytes this rank's GEMM epilogues push to the other ranks per step, against the measured peer-copy rate
-            out_bytes = sum(M * lin.local_rows * 2 for lin in layers) * (world - 1)
-            line["nvlink"] = {"bytes_out_per_rank_per_step": out_bytes,
-                              "achieved_gbs": out_bytes / (ms / args.steps * 1e-3) / 1e9, "peak_gbs": 770.0,
-                              "peak_source": "measured peer copy per direction on this pool",
-                              "note": "whole step in the denominator, quantizer kernels (no traffic) included"}
+        if nvlink is not None:
+            line["nvlink"] = nvlink
         print(json.dumps(line), flush=True)
-    if peers is not None:
-        peers.close()
     if distributed:
         dist.destroy_process_group()
 
@@ -663,7 +1147,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the quantizer bandwidth sweep")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the single-GPU extras: sustained run, FP4 ceiling, quantizer sweep and comparators, "
+                         "small-M sweep, MXFP8")
+    ap.add_argument("--no-wan", action="store_true", help="skip the short record of the Wan-class workload")
+    ap.add_argument("--sustained-seconds", type=float, default=3.0)
+    ap.add_argument("--peer-map-limit-gib", type=int, default=4,
+                    help="N > 1: above this many GiB of peer-mapped output matrices per rank the NCCL all-gather is used")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic stream serialisation")
     ap.add_argument("--dependent-launch-mask", type=int, default=None,

@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "ck_b200_peer_close",
     "ck_b200_peer_free",
     "ck_b200_dynamic_scale_nvfp4",
+    "ck_b200_quantize_nvfp4_dynamic",
     "ck_b200_quantize_mxfp8",
     "ck_b200_dequantize_mxfp8",
     "ck_b200_scaled_mm_mxfp8",
@@ -86,6 +87,8 @@ def load() -> ctypes.CDLL:
     L.ck_b200_scaled_mm_mxfp8.restype = i32
     L.ck_b200_dynamic_scale_nvfp4.argtypes = [vp, i32, i64, vp, vp]
     L.ck_b200_dynamic_scale_nvfp4.restype = i32
+    L.ck_b200_quantize_nvfp4_dynamic.argtypes = [vp, i32, vp, vp, vp, i64, i64, i32, i32, vp, vp]
+    L.ck_b200_quantize_nvfp4_dynamic.restype = i32
     L.ck_b200_last_error.argtypes = []
     L.ck_b200_last_error.restype = ctypes.c_char_p
     L.ck_b200_query.argtypes = [i32]

@@ -42,12 +42,18 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(build_dir, exist_ok=True)
     env = dict(os.environ)
     env.pop("CC", None)
-    for src in SOURCES:
+    def compile_one(src: str):
         obj = os.path.join(build_dir, src.replace(".cu", ".o"))
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
-        r = subprocess.run(cmd, capture_output=True, text=True, env=env)
+        return src, obj, subprocess.run(cmd, capture_output=True, text=True, env=env)
+
+    # the translation units are independent: compile them side by side
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(compile_one, SOURCES))
+    for src, obj, r in results:
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{r.stderr}")
         if verbose:

@@ -13,6 +13,8 @@ std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
 std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
+std::atomic<int> g_quant_sync_test{0};
+std::atomic<int> g_dynamic_fused_max_mb{120};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -95,6 +97,8 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_GEMM_DEBUG: return ckb::g_gemm_debug.exchange(value);
         case CK_B200_TUNE_LINEAR_FUSED: return ckb::g_linear_fused.exchange(value);
         case CK_B200_TUNE_QUANT_FLAT: return ckb::g_quant_flat.exchange(value);
+        case CK_B200_TUNE_QUANT_SYNC_TEST: return ckb::g_quant_sync_test.exchange(value);
+        case CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB: return ckb::g_dynamic_fused_max_mb.exchange(value);
         default: return -1;
     }
 }
@@ -149,12 +153,13 @@ int ck_b200_peer_free(void* ptr) {
 namespace {
 struct LinearPlan {
     int64_t prow;          // activation rows after padding to 16
-    size_t scale_off, q_off, sf_off, sync_off, end;   // byte offsets inside the workspace
+    size_t scale_off, dyn_sync_off, q_off, sf_off, sync_off, end;   // byte offsets inside the workspace
 };
 LinearPlan plan_linear(int64_t M, int64_t K) {
     LinearPlan p;
     p.prow = ckb::round_up64(M, 16);
     p.scale_off = 0;
+    p.dyn_sync_off = 64;   // 16 bytes of counters of the dynamic quantizer: zero once, like the area at sync_off
     // the sync area of the fused kernel sits at the same place for every shape, so that nothing but that kernel
     // ever writes there when linears of different shapes share one workspace
     p.sync_off = 256;
@@ -185,20 +190,29 @@ int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, c
                          "(ck_b200_linear_nvfp4_workspace_bytes)", (long long)p.end);
     char* ws = (char*)workspace_dev;
     const float* ts_x = input_scale_dev_or_null;
-    if (!ts_x) {
-        float* dyn = (float*)(ws + p.scale_off);
-        if (int rc = ck_b200_dynamic_scale_nvfp4(x_dev, x_dtype, M * K, dyn, stream)) return rc;
-        ts_x = dyn;
-    }
+    float* dyn = (float*)(ws + p.scale_off);
     void* qx = ws + p.q_off;
     void* sfx = ws + p.sf_off;
     // on request, for more than one tile row and column: the GEMM kernel quantizes the activations itself
-    if (ckb::g_linear_fused.load() && ckb::g_gemm_variant.load() == 0 &&
-        ckb::fused_linear_supported(x_dtype, x_dev, M, N, K, out_dtype))
+    const bool in_gemm = ckb::g_linear_fused.load() && ckb::g_gemm_variant.load() == 0 &&
+                         ckb::fused_linear_supported(x_dtype, x_dev, M, N, K, out_dtype);
+    if (in_gemm) {
+        if (!ts_x) {
+            if (int rc = ck_b200_dynamic_scale_nvfp4(x_dev, x_dtype, M * K, dyn, stream)) return rc;
+            ts_x = dyn;
+        }
         return ckb::fused_linear_launch(x_dev, x_dtype, M, K, ts_x, qx, sfx, ws + p.sync_off, w_q_dev, w_sf_dev,
                                         w_scale_dev, N, bias_dev_or_null, bias_dtype, out_dev, out_dtype, stream);
-    if (int rc = ck_b200_quantize_nvfp4(x_dev, x_dtype, ts_x, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1, stream))
+    }
+    if (!ts_x) {
+        // no scale given: derived from x like the layout does, in the same launch as the quantizer where x fits the L2
+        if (int rc = ck_b200_quantize_nvfp4_dynamic(x_dev, x_dtype, dyn, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1,
+                                                    ws + p.dyn_sync_off, stream))
+            return rc;
+        ts_x = dyn;
+    } else if (int rc = ck_b200_quantize_nvfp4(x_dev, x_dtype, ts_x, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1, stream)) {
         return rc;
+    }
     // what is left of the workspace serves the split-K reduction of small-M problems
     const size_t rest = workspace_bytes - p.end;
     return ck_b200_scaled_mm_nvfp4(qx, sfx, w_q_dev, w_sf_dev, ts_x, w_scale_dev, nullptr, bias_dev_or_null, bias_dtype,

@@ -32,6 +32,10 @@ int check_device(int* sm_count_out);
 // path, the bytes of its sync area, and the launch.  qx / sfx receive the quantized activations (rows padded to 16).
 extern std::atomic<int> g_linear_fused;
 extern std::atomic<int> g_quant_flat;   // 0 = off, else the least units per warp for the one-wave quantizer geometry
+extern std::atomic<int> g_quant_sync_test;       // > 0: the dynamic quantizer expects that many arrivals too many (tests)
+extern std::atomic<int> g_dynamic_fused_max_mb;  // largest input (10^6 bytes) the dynamic quantizer handles in one launch
+// Status word of the quantizer kernels (its own translation unit): reads and clears it.
+int read_quant_status(int* out);
 bool fused_linear_supported(int x_dtype, const void* x_dev, int64_t M, int64_t N, int64_t K, int out_dtype);
 size_t fused_sync_bytes();
 int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, const float* ts_x_dev, void* qx_dev,

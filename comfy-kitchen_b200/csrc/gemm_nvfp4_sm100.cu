@@ -1784,6 +1784,9 @@ extern "C" int ck_b200_read_device_status(int* status_out) {
     CKB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
     const int zero = 0;
     CKB_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    int vq = 0;   // the quantizer kernels keep their own word (another translation unit)
+    if (int rc = read_quant_status(&vq)) return rc;
+    if (v == 0) v = vq;
     *status_out = v;
     return v == 0 ? CK_B200_OK : fail(CK_B200_ERR_DEVICE_STATUS, "a kernel gave up on bounded wait %d", v);
 }

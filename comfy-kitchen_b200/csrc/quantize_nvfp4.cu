@@ -15,6 +15,8 @@
 // with 16-byte aligned groups of four 4-byte stores and no separate layout pass or memset.
 // Lane l owns row r0 + 32*(l/8) and the 8 elements at column 64*cbg + 8*(l%8): a warp load covers
 // four fully used 128-byte lines (16-bit inputs), a warp store four full 32-byte sectors of packed output.
+#include <mutex>
+
 #include "quantize_nvfp4_device.cuh"
 
 namespace ckb {
@@ -297,6 +299,182 @@ __global__ void finalize_scale_kernel(float* scale) {
     *scale = Output<DT>::round(__fdiv_rn(*scale, 2688.0f));
 }
 
+// ---- per-tensor scale and quantization in one launch --------------------------------------------------------
+//
+// TensorCoreNVFP4Layout.quantize derives the per-tensor scale from the tensor itself when the caller gives none
+// (comfy_kitchen/tensor/nvfp4.py:66-71): amax(|x|) / (448 * 6) in x's dtype.  As separate kernels that is a full read
+// of x from HBM for the maximum and a second one for the quantizer.  quantize_nvfp4_dynamic_kernel does both in one
+// launch of the one-wave geometry above: every warp first takes the maximum over the range of units it will
+// quantize (which leaves x in the 126 MB L2), the blocks meet at a grid-wide counter, and every warp then
+// quantizes its range from L2 with the scale all blocks now agree on.  The grid never exceeds the blocks that are
+// resident at once, so the blocks can wait for one another; the wait is bounded all the same (about a second),
+// after which the block records WAIT_QUANT_GRID in the status word and returns without quantizing.
+//
+// DynamicSync lives in 16 bytes of caller memory that are zero before the first launch; the last block past the
+// meeting point leaves them zero again, so any sequence of launches and graph replays on one stream works.
+struct DynamicSync {
+    uint32_t amax_bits;   // bits of the running maximum (non-negative floats order like their bits)
+    uint32_t arrived;     // blocks that have contributed their maximum
+    uint32_t departed;    // blocks that have read the final maximum
+    uint32_t pad;
+};
+constexpr int WAIT_QUANT_GRID = 8;
+__device__ int g_quant_status = 0;
+
+template <int DT>
+__device__ __forceinline__ float raw_amax(const typename Input<DT>::Raw& r) {
+    if constexpr (DT == CK_B200_DTYPE_BF16) {
+        const uint32_t p = maxabs_bf16x2(maxabs_bf16x2(r.v.x, r.v.y), maxabs_bf16x2(r.v.z, r.v.w));
+        return fmaxf(__uint_as_float((p << 16) & 0x7fff0000u), __uint_as_float(p & 0x7fff0000u));
+    } else {
+        return Pairs<DT>::half_amax(r);
+    }
+}
+
+// Maximum of |x| over the part of units [pos, end) of the flat unit sequence that this lane owns.
+template <int DT>
+__device__ __forceinline__ float range_amax(const QuantArgs& a, long long pos, long long end, int lane) {
+    using In = Input<DT>;
+    constexpr int kUnitBytes = 64 * In::kBytes;
+    float m = 0.0f;
+    const int sub = lane & 7;
+    while (pos < end) {
+        const int gi = (int)(pos / a.sf_cbg);
+        const int u0 = (int)(pos - (long long)gi * a.sf_cbg);
+        const int u1 = (int)min((long long)a.sf_cbg, (long long)u0 + (end - pos));
+        const int group = a.row_groups - 1 - gi;
+        const int r = (group >> 5) * 128 + (group & 31) + 32 * (lane >> 3);
+        if (r < a.rows) {
+            const char* p = (const char*)a.x + ((int64_t)r * a.cols + sub * 8) * In::kBytes;
+            // units whose eight columns of this lane lie inside the row (cols is a multiple of 8 on this path)
+            const int u_in = min(u1, (a.cols - sub * 8 + 63) / 64);
+            int u = u0;
+            for (; u + 4 <= u_in; u += 4) {
+                const typename In::Raw r0 = In::load_vec(p + (int64_t)u * kUnitBytes),
+                                       r1 = In::load_vec(p + (int64_t)(u + 1) * kUnitBytes),
+                                       r2 = In::load_vec(p + (int64_t)(u + 2) * kUnitBytes),
+                                       r3 = In::load_vec(p + (int64_t)(u + 3) * kUnitBytes);
+                m = fmaxf(fmaxf(m, fmaxf(raw_amax<DT>(r0), raw_amax<DT>(r1))), fmaxf(raw_amax<DT>(r2), raw_amax<DT>(r3)));
+            }
+            for (; u < u_in; ++u) m = fmaxf(m, raw_amax<DT>(In::load_vec(p + (int64_t)u * kUnitBytes)));
+        }
+        pos += u1 - u0;
+    }
+    return m;
+}
+
+template <int DT, int VARIANT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, kBlocksPerSM)
+quantize_nvfp4_dynamic_kernel(const QuantArgs a, float* __restrict__ scale_out, DynamicSync* __restrict__ sync, int per_warp,
+                              long long total_units, unsigned expected_blocks, long long wait_cycles) {
+    allow_dependent_launch();
+    __shared__ float s_max[kWarpsPerBlock];
+    __shared__ float s_ts;
+    const int lane = threadIdx.x, warp = threadIdx.y;
+    const long long pos = ((long long)blockIdx.x * kWarpsPerBlock + warp) * per_warp;
+    const long long end = min(total_units, pos + per_warp);
+    grid_dependency_wait();
+    // phase 1: this warp's share of the maximum
+    float m = pos < end ? range_amax<DT>(a, pos, end, lane) : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) s_max[warp] = m;
+    __syncthreads();
+    if (warp == 0 && lane == 0) {
+        float bm = s_max[0];
+#pragma unroll
+        for (int w = 1; w < kWarpsPerBlock; ++w) bm = fmaxf(bm, s_max[w]);
+        atomicMax(&sync->amax_bits, __float_as_uint(bm));
+        __threadfence();
+        atomicAdd(&sync->arrived, 1u);
+        // meeting point: every block of the grid has contributed
+        float ts = -1.0f;   // negative: the wait ran out
+        const long long start = clock64();
+        for (;;) {
+            uint32_t n;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(&sync->arrived) : "memory");
+            if (n >= expected_blocks) {
+                uint32_t bits;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(bits) : "l"(&sync->amax_bits) : "memory");
+                // amax / (448 * 6) evaluated in the input dtype (comfy_kitchen/tensor/nvfp4.py:66-71)
+                ts = Output<DT>::round(__fdiv_rn(__uint_as_float(bits), 2688.0f));
+                break;
+            }
+            if (clock64() - start > wait_cycles) {
+                atomicCAS(&g_quant_status, 0, WAIT_QUANT_GRID);
+                break;
+            }
+            __nanosleep(64);
+        }
+        if (ts >= 0.0f) {
+            if (blockIdx.x == 0) *scale_out = ts;
+            // the last block past the meeting point leaves the counters zero for the next launch
+            if (atomicAdd(&sync->departed, 1u) + 1u == expected_blocks) {
+                sync->amax_bits = 0u;
+                sync->departed = 0u;
+                __threadfence();
+                sync->arrived = 0u;
+            }
+        }
+        s_ts = ts;
+    }
+    __syncthreads();
+    const float ts = s_ts;
+    if (ts < 0.0f || pos >= end) return;
+    // phase 2: the quantizer's walk over the same range, now served by L2
+    long long p = pos;
+    while (p < end) {
+        const int gi = (int)(p / a.sf_cbg);
+        const int u0 = (int)(p - (long long)gi * a.sf_cbg);
+        const int u1 = (int)min((long long)a.sf_cbg, (long long)u0 + (end - p));
+        quantize_units<DT, true, VARIANT>(a, u0, u1, a.row_groups - 1 - gi, lane, ts);
+        p += u1 - u0;
+    }
+}
+
+
+// Resident blocks of the dynamic kernel per SM (cached per device and dtype); never more than kBlocksPerSM.
+template <int DT>
+int dynamic_blocks_per_sm(int* out) {
+    static std::mutex mu;
+    static int cache[64] = {0};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == 0) {
+        int n = 0;
+        CKB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_nvfp4_dynamic_kernel<DT, 2>,
+                                                                  kWarpsPerBlock * 32, 0));
+        cache[dev] = n < 1 ? -1 : (n > kBlocksPerSM ? kBlocksPerSM : n);
+    }
+    if (cache[dev] < 0) return fail(CK_B200_ERR_CUDA, "the dynamic quantizer kernel does not fit on this device");
+    *out = cache[dev];
+    return CK_B200_OK;
+}
+
+template <int DT>
+int launch_quantize_dynamic(QuantArgs a, float* scale_out, void* sync, int sms, cudaStream_t stream) {
+    int per_sm = 0;
+    if (int rc = dynamic_blocks_per_sm<DT>(&per_sm)) return rc;
+    const long long total = (long long)a.row_groups * a.sf_cbg;
+    const long long resident_warps = (long long)per_sm * sms * kWarpsPerBlock;
+    int per_warp = (int)round_up64(ceil_div64(total, resident_warps), 2);
+    if (per_warp < 2) per_warp = 2;
+    const unsigned blocks = (unsigned)ceil_div64(ceil_div64(total, per_warp), kWarpsPerBlock);
+    a.seg_units = a.sf_cbg;
+    a.segments = 1;
+    // test hook: expect arrivals that never come and give up after about 0.1 s instead of 1 s
+    const int extra = g_quant_sync_test.load();
+    const long long wait_cycles = extra > 0 ? 200000000ll : 2000000000ll;
+    const cudaError_t err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_dynamic_kernel<DT, 2>, dim3(blocks),
+                                             dim3(32, kWarpsPerBlock), 0, stream, a, scale_out, (DynamicSync*)sync, per_warp,
+                                             total, blocks + (unsigned)(extra > 0 ? extra : 0), wait_cycles);
+    g_launches.fetch_add(1);
+    CKB_CUDA_OK(err);
+    return CK_B200_OK;
+}
+
 }  // namespace
 }  // namespace ckb
 
@@ -414,4 +592,69 @@ extern "C" int ck_b200_dynamic_scale_nvfp4(const void* x_dev, int x_dtype, int64
     g_launches.fetch_add(1);
     CKB_CUDA_OK(cudaGetLastError());
     return CK_B200_OK;
+}
+
+namespace ckb {
+int read_quant_status(int* out) {
+    int v = 0;
+    CKB_CUDA_OK(cudaMemcpyFromSymbol(&v, g_quant_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        CKB_CUDA_OK(cudaMemcpyToSymbol(g_quant_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return CK_B200_OK;
+}
+}  // namespace ckb
+
+extern "C" int ck_b200_quantize_nvfp4_dynamic(const void* x_dev, int x_dtype, float* scale_out_dev, void* q_out_dev,
+                                              void* sf_out_dev, int64_t rows, int64_t cols, int pad_16x, int hi_first,
+                                              void* sync_dev, void* stream) {
+    int sms = 0;
+    if (int rc = check_device(&sms)) return rc;
+    if (!x_dev || !scale_out_dev || !q_out_dev || !sf_out_dev)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4_dynamic: null pointer");
+    if (rows < 0 || cols < 0 || rows > 0x3fffff00ll || cols > 0x3fffff00ll)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4_dynamic: rows and cols must be in [0, 2^30)");
+    if (!pad_16x && (rows % 16 != 0 || cols % 16 != 0))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT,
+                    "quantize_nvfp4_dynamic: rows and cols must be divisible by 16 without pad_16x, got %lld x %lld",
+                    (long long)rows, (long long)cols);
+    if (x_dtype < 0 || x_dtype > 2)
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4_dynamic: dtype code %d", x_dtype);
+    if (sync_dev && ((uintptr_t)sync_dev & 15))
+        return fail(CK_B200_ERR_INVALID_ARGUMENT, "quantize_nvfp4_dynamic: the sync words must be 16-byte aligned");
+    const int64_t prow = pad_16x ? round_up64(rows, 16) : rows, pcol = pad_16x ? round_up64(cols, 16) : cols;
+    const int64_t sf_cbg = round_up64(pcol / 16, 4) / 4;
+    const int64_t in_bytes = rows * cols * (x_dtype == CK_B200_DTYPE_F32 ? 4 : 2);
+    const bool vec = (cols % 8 == 0) && (((uintptr_t)x_dev & 15) == 0);
+    // one launch while x fits the L2 (the second pass then reads it from there) and the one-wave geometry applies;
+    // otherwise the reduction kernel, the scale and the quantizer as separate launches: same bits either way
+    const bool one_launch = sync_dev && vec && sf_cbg % 2 == 0 && prow > 0 && pcol > 0 && g_quant_variant.load() == 2 &&
+                            in_bytes <= (int64_t)g_dynamic_fused_max_mb.load() * 1000000ll &&
+                            !(((uintptr_t)q_out_dev & 3) || ((uintptr_t)sf_out_dev & 3));
+    if (!one_launch) {
+        if (int rc = ck_b200_dynamic_scale_nvfp4(x_dev, x_dtype, rows * cols, scale_out_dev, stream)) return rc;
+        return ck_b200_quantize_nvfp4(x_dev, x_dtype, scale_out_dev, q_out_dev, sf_out_dev, rows, cols, pad_16x, hi_first,
+                                      stream);
+    }
+    QuantArgs a;
+    a.x = x_dev;
+    a.pts = scale_out_dev;   // not read by the kernel: the scale is handed over inside it
+    a.q = (uint8_t*)q_out_dev;
+    a.sf = (uint8_t*)sf_out_dev;
+    a.rows = (int)rows;
+    a.cols = (int)cols;
+    a.prow = (int)prow;
+    a.pcol = (int)pcol;
+    a.row_groups = (int)(round_up64(prow, 128) / 4);
+    a.sf_cbg = (int)sf_cbg;
+    a.seg_units = a.segments = 0;
+    a.hi_first = hi_first ? 1 : 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case CK_B200_DTYPE_F32: return launch_quantize_dynamic<CK_B200_DTYPE_F32>(a, scale_out_dev, sync_dev, sms, s);
+        case CK_B200_DTYPE_F16: return launch_quantize_dynamic<CK_B200_DTYPE_F16>(a, scale_out_dev, sync_dev, sms, s);
+        default: return launch_quantize_dynamic<CK_B200_DTYPE_BF16>(a, scale_out_dev, sync_dev, sms, s);
+    }
 }

@@ -16,18 +16,27 @@ from . import _lib
 DTYPE_TO_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}  # eager/quantization.py:34-42
 
 
-_WORKSPACES: dict[int, torch.Tensor] = {}
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
 _WORKSPACE_BYTES = 32 << 20   # the reference keeps a 32 MiB cuBLAS workspace per device (backends/cuda/__init__.py:444-462)
 
 
-def _workspace(device: torch.device) -> torch.Tensor:
-    """Per-device scratch for split-K partial sums (problems with M <= 128), allocated once through torch's caching
-    allocator so that calls stay allocation-free afterwards."""
+def _stream_key(device: torch.device) -> tuple[int, int]:
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _WORKSPACES.get(idx)
+    return idx, int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _workspace(device: torch.device) -> torch.Tensor | None:
+    """Scratch for split-K partial sums (problems with M <= 128): one buffer per (device, stream), so that calls on
+    different streams never share partial sums, allocated once through torch's caching allocator so that calls stay
+    allocation-free afterwards.  Returns None while the stream is being captured and has no buffer yet (nothing is
+    allocated inside a capture: the GEMM then runs unsplit); one call on that stream before the capture avoids that."""
+    key = _stream_key(device)
+    ws = _WORKSPACES.get(key)
     if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
         ws = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
-        _WORKSPACES[idx] = ws
+        _WORKSPACES[key] = ws
     return ws
 
 
@@ -92,6 +101,54 @@ def quantize_nvfp4(x: torch.Tensor, per_tensor_scale: torch.Tensor, epsilon: flo
                                                 orig_cols, int(bool(pad_16x)), int(bool(hi_first)), _stream(x.device))
     _lib.check(rc, "quantize_nvfp4")
     return qx, sx.view(torch.float8_e4m3fn)
+
+
+_DYN_SYNC: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _dynamic_sync(device: torch.device) -> torch.Tensor | None:
+    """The 16 zeroed bytes the one-launch dynamic quantizer meets at, one set per (device, stream).  None while the
+    stream is being captured and has none yet (the call then takes the separate kernels: same bits)."""
+    key = _stream_key(device)
+    t = _DYN_SYNC.get(key)
+    if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        t = torch.zeros(64, dtype=torch.uint8, device=device)
+        _DYN_SYNC[key] = t
+    return t
+
+
+def quantize_nvfp4_dynamic(x: torch.Tensor, pad_16x: bool = False, hi_first: bool = True,
+                           _sync: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """quantize_nvfp4 with the per-tensor scale ``TensorCoreNVFP4Layout.quantize`` derives when none is given
+    (``comfy_kitchen/tensor/nvfp4.py:53-84``: amax(|x|)/(448*6) in x's dtype), without a separate pass over x where x
+    fits the L2: returns (packed bytes, tiled block scales, the float32 scale), bit-identical to
+    ``dynamic_scale_nvfp4`` followed by ``quantize_nvfp4``."""
+    x = _plain(x)
+    _require_cuda(x, "x")
+    if x.dim() != 2:
+        raise ValueError(f"quantize_nvfp4_dynamic needs a 2D tensor, got {x.dim()}D")
+    if x.dtype not in DTYPE_TO_CODE:
+        raise TypeError(f"quantize_nvfp4_dynamic: unsupported dtype {x.dtype}")
+    assert x.is_contiguous(), "Input tensor must be contiguous"
+    orig_rows, orig_cols = x.shape
+    if pad_16x:
+        num_rows, num_cols = roundup(orig_rows, 16), roundup(orig_cols, 16)
+    else:
+        num_rows, num_cols = orig_rows, orig_cols
+        assert num_rows % 16 == 0, f"num_rows must be divisible by 16, got {num_rows}"
+        assert num_cols % 16 == 0, f"num_cols must be divisible by 16, got {num_cols}"
+    with torch.cuda.device(x.device):
+        scale = torch.empty((), device=x.device, dtype=torch.float32)
+        qx = torch.empty((num_rows, num_cols // 2), device=x.device, dtype=torch.uint8)
+        sx = torch.empty((roundup(num_rows, 128), roundup(num_cols // 16, 4)), device=x.device, dtype=torch.uint8)
+        sync = _sync if _sync is not None else _dynamic_sync(x.device)
+        rc = _lib.load().ck_b200_quantize_nvfp4_dynamic(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(scale), _ptr(qx), _ptr(sx),
+                                                        orig_rows, orig_cols, int(bool(pad_16x)), int(bool(hi_first)),
+                                                        _ptr(sync), _stream(x.device))
+    _lib.check(rc, "quantize_nvfp4_dynamic")
+    return qx, sx.view(torch.float8_e4m3fn), scale
 
 
 def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_scales: torch.Tensor,
@@ -337,7 +394,7 @@ def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
     return out
 
 
-_LINEAR_WS: dict[int, torch.Tensor] = {}
+_LINEAR_WS: dict[tuple[int, int], torch.Tensor] = {}
 
 
 def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: torch.Tensor, weight_scale: torch.Tensor,
@@ -346,7 +403,10 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
     """y[M, N] = x[M, K] @ W^T + bias with W resident in NVFP4: the activation scale (``input_scale`` or the layout's
     dynamic one), the quantization of x and the GEMM are enqueued by one library call, with the quantized activation
     in a per-device workspace that grows on demand.  Same arithmetic as dynamic_scale_nvfp4 -> quantize_nvfp4(pad_16x)
-    -> scaled_mm_nvfp4, so results are bit-identical to calling those three."""
+    -> scaled_mm_nvfp4, so results are bit-identical to calling those three.  The workspace (quantized activation,
+    its scales, split-K partial sums) is kept per (device, stream): calls on one stream are ordered, calls on different
+    streams use different buffers.  It cannot grow while the stream is being captured: call once with the largest
+    shape before capturing."""
     x = _plain(x)
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype not in DTYPE_TO_CODE:
@@ -369,13 +429,19 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
     if need < 0:
         raise RuntimeError(f"linear_nvfp4: K = {k} must be a multiple of 32")
     need += _WORKSPACE_BYTES if m <= 128 else 0
-    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
-    ws = _LINEAR_WS.get(idx)
+    key = _stream_key(x.device)
+    ws = _LINEAR_WS.get(key)
     with torch.cuda.device(x.device):
         if ws is None or ws.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("linear_nvfp4: the workspace of this stream must grow, which cannot happen inside a "
+                                   "stream capture; call once with this shape on this stream before capturing")
+            old = ws
             ws = torch.empty(max(need, 64 << 20), dtype=torch.uint8, device=x.device)
             ws[: 1 << 16].zero_()      # the fused kernel's progress words start from zero
-            _LINEAR_WS[idx] = ws
+            _LINEAR_WS[key] = ws
+            if old is not None:
+                old.record_stream(torch.cuda.current_stream(x.device))   # earlier calls on this stream may still read it
         w_ts = _scale_on(x.device, weight_scale)
         in_ts = None if input_scale is None else _scale_on(x.device, input_scale)
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)

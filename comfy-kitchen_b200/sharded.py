@@ -202,6 +202,22 @@ class ShardedNVFP4Linear:
         self.input_scale = None if inp is None else inp.to(device=dev, dtype=torch.float32).reshape(())
         return self
 
+    def quantize_input(self, x: torch.Tensor):
+        """The activation as the GEMM wants it: (packed bytes, tiled block scales, per-tensor scale), rows padded to 16.
+        Split from the GEMM so that a caller can put the two on different streams."""
+        pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
+        if self.input_scale is None and hasattr(self.ops, "quantize_nvfp4_dynamic"):
+            return self.ops.quantize_nvfp4_dynamic(x, pad_16x=pad)     # scale and quantization in one launch
+        ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
+        qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
+        return qx, sfx, ts_x
+
+    def local_from_quantized(self, qx: torch.Tensor, sfx: torch.Tensor, ts_x: torch.Tensor, rows: int,
+                             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        y = self.ops.scaled_mm_nvfp4(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
+                                     bias=self.bias, out_dtype=out_dtype)
+        return y[:rows, : self.local_rows]
+
     def local(self, x: torch.Tensor, one_call: bool = False) -> torch.Tensor:
         """This rank's [M, n1-n0] block of the output.  ``one_call``: through the library's whole-linear entry point
         (same bits; for more than 128 rows and columns the GEMM kernel then quantizes x itself)."""
@@ -209,12 +225,9 @@ class ShardedNVFP4Linear:
             y = self.ops.linear_nvfp4(x, self.qweight, self.weight_block_scale, self.weight_scale,
                                       input_scale=self.input_scale, bias=self.bias)
             return y[:, : self.local_rows]
-        ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
-        pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
-        qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
-        y = self.ops.scaled_mm_nvfp4(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
-                                     bias=self.bias, out_dtype=x.dtype if x.dtype != torch.float32 else torch.bfloat16)
-        return y[: x.shape[0], : self.local_rows]
+        qx, sfx, ts_x = self.quantize_input(x)
+        return self.local_from_quantized(qx, sfx, ts_x, x.shape[0],
+                                         out_dtype=x.dtype if x.dtype != torch.float32 else torch.bfloat16)
 
     def bind(self, peers: PeerGroup, m: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         """Set up the fused path for activations of ``m`` rows: allocates this layer's [m, N] output matrix on every
@@ -228,18 +241,19 @@ class ShardedNVFP4Linear:
         self.out_full = self._out_mem.tensor((m, self.out_features), dtype)
         return self.out_full
 
+    def fused_from_quantized(self, qx: torch.Tensor, sfx: torch.Tensor, ts_x: torch.Tensor, rows: int) -> torch.Tensor:
+        assert rows == self._out_rows, "bind() fixed the number of rows"
+        self.ops.scaled_mm_nvfp4_all_gather(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
+                                            self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias,
+                                            rows=rows)
+        return self.out_full
+
     def fused(self, x: torch.Tensor) -> torch.Tensor:
         """Quantize, multiply by this rank's shard and store the column block into every rank's output matrix from
         the GEMM's epilogue.  Returns this rank's matrix, complete after the next ``peers.barrier()`` on all ranks;
         a barrier must also separate a consumer of the matrix from the next call that overwrites it."""
-        assert x.shape[0] == self._out_rows, "bind() fixed the number of rows"
-        ts_x = self.input_scale if self.input_scale is not None else self.ops.dynamic_scale_nvfp4(x)
-        pad = x.shape[0] % 16 != 0 or x.shape[1] % 16 != 0
-        qx, sfx = self.ops.quantize_nvfp4(x, ts_x, pad_16x=pad)
-        self.ops.scaled_mm_nvfp4_all_gather(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
-                                            self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias,
-                                            rows=x.shape[0])
-        return self.out_full
+        qx, sfx, ts_x = self.quantize_input(x)
+        return self.fused_from_quantized(qx, sfx, ts_x, x.shape[0])
 
     def gather_async(self, y_local: torch.Tensor):
         """Start the all-gather of equal column blocks and return ``(work, buffer)``: the collective runs on the

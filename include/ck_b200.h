@@ -163,7 +163,8 @@ int ck_b200_peer_free(void* ptr);
  * and bf16 / fp16 activations the call is ONE kernel: the CTA-pair GEMM carries eight extra warps per CTA that
  * quantize x into the workspace while the tensor-core main loop runs, and each tile's loads wait (bounded) for the
  * 128-row band of x they read.  Results are bit-identical to the separate operators.  The progress
- * words live in bytes [256, 256 + 32 KiB) of the workspace, which only that kernel writes: zero them once when the
+ * words live in bytes [256, 256 + 32 KiB) of the workspace, which only that kernel writes, and the counters of the
+ * dynamic quantizer (input_scale_dev_or_null == NULL) in bytes [64, 80): zero the first 33 KiB once when the
  * workspace is allocated (they then stay consistent over any sequence of calls, shapes and graph replays).  Calls
  * that share a workspace must not overlap on the GPU.
  */
@@ -201,6 +202,24 @@ int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, const void* 
  */
 int ck_b200_dynamic_scale_nvfp4(const void* x_dev, int x_dtype, int64_t numel, float* scale_out_dev, void* stream);
 
+/*
+ * quantize_nvfp4 with the per-tensor scale derived from x itself, as TensorCoreNVFP4Layout.quantize does when the
+ * caller gives none (comfy_kitchen/tensor/nvfp4.py:53-84: scale = amax(|x|) / (448*6) in x's dtype, then
+ * ck.quantize_nvfp4(x, scale)).  Same outputs, bit for bit, as ck_b200_dynamic_scale_nvfp4 followed by
+ * ck_b200_quantize_nvfp4; scale_out_dev receives the float32 scale (the GEMM's tensor_scale_a).
+ * While x fits the L2 (CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB, default 120) this is ONE kernel launch: every warp takes the
+ * maximum over the part of x it will quantize, the blocks meet at a grid-wide counter, then quantize from L2 - the
+ * second read of x from HBM is gone.  Larger or oddly shaped inputs (columns not a multiple of 128, unaligned base)
+ * take the separate kernels inside the same call.
+ *   sync_dev   16 bytes, 16-byte aligned, zero before the first call; the kernel leaves them zero.  Calls that share
+ *              them must be ordered on one stream.  NULL selects the separate kernels.
+ * The meeting point is a bounded wait (about a second): if it runs out, the blocks record code 8 in the status word
+ * (ck_b200_read_device_status) and return without writing the outputs.
+ */
+int ck_b200_quantize_nvfp4_dynamic(const void* x_dev, int x_dtype, float* scale_out_dev, void* q_out_dev,
+                                   void* sf_out_dev, int64_t rows, int64_t cols, int pad_16x, int hi_first,
+                                   void* sync_dev, void* stream);
+
 /* Message describing the calling thread's last failure ("" if none).  Counterpart of the
  * std::runtime_error text of the reference launchers (comfy_kitchen/backends/cuda/ops/quantize_nvfp4.cu:380-383). */
 const char* ck_b200_last_error(void);
@@ -233,6 +252,10 @@ int ck_b200_read_device_status(int* status_out);
                                         when the shape allows it (default 0: separate kernels, which measured faster) */
 #define CK_B200_TUNE_QUANT_FLAT 5     /* quantize_nvfp4 launch geometry: 0 = segments of rows in several waves; n > 0
                                         (default 12) = one wave of equal ranges when every resident warp gets n to 128 units */
+#define CK_B200_TUNE_QUANT_SYNC_TEST 6 /* tests only: n > 0 makes the dynamic quantizer wait for n blocks that do not
+                                        exist and give up after about 0.1 s (the wait then runs out by design) */
+#define CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB 7 /* largest input, in 10^6 bytes, that ck_b200_quantize_nvfp4_dynamic handles
+                                             in one launch (default 120: what stays in the 126 MB L2) */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus

@@ -398,6 +398,15 @@ int mxfp8_oracle_dequantize(const uint8_t* q, const uint8_t* sf, int64_t rows, i
     return 0;
 }
 
+/* Number of OpenMP threads the loops above use from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void nvfp4_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int nvfp4_oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -60,6 +60,8 @@ def lib() -> ctypes.CDLL:
         L.mxfp8_oracle_dequantize.restype = i32
         L.nvfp4_oracle_num_threads.argtypes = []
         L.nvfp4_oracle_num_threads.restype = i32
+        L.nvfp4_oracle_set_num_threads.argtypes = [i32]
+        L.nvfp4_oracle_set_num_threads.restype = None
         _lib = L
     return _lib
 
@@ -74,6 +76,24 @@ def roundup(x: int, m: int) -> int:
 
 def num_threads() -> int:
     return int(lib().nvfp4_oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Make the oracle's OpenMP loops, numpy's BLAS and torch use every core this process may run on, whatever
+    OMP_NUM_THREADS the launcher exported (torchrun sets it to 1), and return that count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().nvfp4_oracle_set_num_threads(n)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)      # numpy's BLAS (the fp32 matmul of the GEMM restatement)
+    except Exception:
+        pass
+    try:
+        import torch
+        torch.set_num_threads(n)
+    except Exception:
+        pass
+    return n
 
 
 def _check_input(x: np.ndarray, dtype: int) -> np.ndarray:
