@@ -15,6 +15,7 @@ std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
 std::atomic<int> g_dynamic_fused_max_mb{120};
+std::atomic<int> g_dynamic_smem{1};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -99,6 +100,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_QUANT_FLAT: return ckb::g_quant_flat.exchange(value);
         case CK_B200_TUNE_QUANT_SYNC_TEST: return ckb::g_quant_sync_test.exchange(value);
         case CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB: return ckb::g_dynamic_fused_max_mb.exchange(value);
+        case CK_B200_TUNE_DYNAMIC_SMEM: return ckb::g_dynamic_smem.exchange(value);
         default: return -1;
     }
 }

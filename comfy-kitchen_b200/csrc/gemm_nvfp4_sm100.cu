@@ -1111,17 +1111,28 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 emit(0, s0, v0);
                 emit(1, s1, v1);
             }
+            {
+                // the other six steps, two register sets deep: the fetch of step i + 1 is in flight while step i is
+                // converted and stored, and the accumulator goes back to the MMA warp as soon as the last fetch
+                // has landed in registers, before the last step's output work
+                uint32_t va[32], vb[32];
+                tc_ld32(t_acc + step_at(2) * EPI_COLS, va);
 #pragma unroll 1
-            for (int i = 2; i < kSteps; ++i) {
-                const int s = step_at(i);
-                uint32_t v[32];
-                tc_ld32(t_acc + s * EPI_COLS, v);
-                tc_wait_ld();
-                emit(i, s, v);
+                for (int i = 2; i < kSteps; i += 2) {
+                    tc_wait_ld();
+                    tc_ld32(t_acc + step_at(i + 1) * EPI_COLS, vb);
+                    emit(i, step_at(i), va);
+                    tc_wait_ld();
+                    if (i + 2 < kSteps) {
+                        tc_ld32(t_acc + step_at(i + 2) * EPI_COLS, va);
+                    } else {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
+                    }
+                    emit(i + 1, step_at(i + 1), vb);
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty0 + acc * 8);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }

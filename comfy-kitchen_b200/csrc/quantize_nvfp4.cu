@@ -321,6 +321,45 @@ struct DynamicSync {
 constexpr int WAIT_QUANT_GRID = 8;
 __device__ int g_quant_status = 0;
 
+// The grid-wide meeting point of the dynamic quantizer, run by one thread per block: contributes the block's maximum,
+// waits (bounded) until every block has, and returns the per-tensor scale amax / (448 * 6) evaluated in the input
+// dtype (comfy_kitchen/tensor/nvfp4.py:66-71), or a negative value when the wait ran out (WAIT_QUANT_GRID is then in
+// the status word).  Block 0 publishes the scale; the last block past the point leaves the counters zero.
+template <int DT>
+__device__ __forceinline__ float grid_meet(DynamicSync* sync, float block_max, unsigned expected_blocks, long long wait_cycles,
+                                           float* scale_out) {
+    atomicMax(&sync->amax_bits, __float_as_uint(block_max));
+    __threadfence();
+    atomicAdd(&sync->arrived, 1u);
+    float ts = -1.0f;
+    const long long start = clock64();
+    for (;;) {
+        uint32_t n;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(&sync->arrived) : "memory");
+        if (n >= expected_blocks) {
+            uint32_t bits;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(bits) : "l"(&sync->amax_bits) : "memory");
+            ts = Output<DT>::round(__fdiv_rn(__uint_as_float(bits), 2688.0f));
+            break;
+        }
+        if (clock64() - start > wait_cycles) {
+            atomicCAS(&g_quant_status, 0, WAIT_QUANT_GRID);
+            break;
+        }
+        __nanosleep(64);
+    }
+    if (ts >= 0.0f) {
+        if (blockIdx.x == 0) *scale_out = ts;
+        if (atomicAdd(&sync->departed, 1u) + 1u == expected_blocks) {
+            sync->amax_bits = 0u;
+            sync->departed = 0u;
+            __threadfence();
+            sync->arrived = 0u;
+        }
+    }
+    return ts;
+}
+
 template <int DT>
 __device__ __forceinline__ float raw_amax(const typename Input<DT>::Raw& r) {
     if constexpr (DT == CK_B200_DTYPE_BF16) {
@@ -384,39 +423,7 @@ quantize_nvfp4_dynamic_kernel(const QuantArgs a, float* __restrict__ scale_out, 
         float bm = s_max[0];
 #pragma unroll
         for (int w = 1; w < kWarpsPerBlock; ++w) bm = fmaxf(bm, s_max[w]);
-        atomicMax(&sync->amax_bits, __float_as_uint(bm));
-        __threadfence();
-        atomicAdd(&sync->arrived, 1u);
-        // meeting point: every block of the grid has contributed
-        float ts = -1.0f;   // negative: the wait ran out
-        const long long start = clock64();
-        for (;;) {
-            uint32_t n;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(&sync->arrived) : "memory");
-            if (n >= expected_blocks) {
-                uint32_t bits;
-                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(bits) : "l"(&sync->amax_bits) : "memory");
-                // amax / (448 * 6) evaluated in the input dtype (comfy_kitchen/tensor/nvfp4.py:66-71)
-                ts = Output<DT>::round(__fdiv_rn(__uint_as_float(bits), 2688.0f));
-                break;
-            }
-            if (clock64() - start > wait_cycles) {
-                atomicCAS(&g_quant_status, 0, WAIT_QUANT_GRID);
-                break;
-            }
-            __nanosleep(64);
-        }
-        if (ts >= 0.0f) {
-            if (blockIdx.x == 0) *scale_out = ts;
-            // the last block past the meeting point leaves the counters zero for the next launch
-            if (atomicAdd(&sync->departed, 1u) + 1u == expected_blocks) {
-                sync->amax_bits = 0u;
-                sync->departed = 0u;
-                __threadfence();
-                sync->arrived = 0u;
-            }
-        }
-        s_ts = ts;
+        s_ts = grid_meet<DT>(sync, bm, expected_blocks, wait_cycles, scale_out);
     }
     __syncthreads();
     const float ts = s_ts;
@@ -432,6 +439,113 @@ quantize_nvfp4_dynamic_kernel(const QuantArgs a, float* __restrict__ scale_out, 
     }
 }
 
+
+// The same for activations small enough to be held on chip between the two phases (up to about 32 MB of 16-bit
+// input: 18 units per warp, 72 KB of shared memory per block, three blocks per SM): phase 1 parks each warp's range in
+// shared memory while taking the maximum, phase 2 quantizes from there, so x is read from HBM once and from nowhere
+// else.  Interior shapes only (rows and columns multiples of 128: no padding rows, whole pairs of units).
+template <int DT>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, kBlocksPerSM)
+quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_out, DynamicSync* __restrict__ sync, int per_warp,
+                                   long long total_units, unsigned expected_blocks, long long wait_cycles) {
+    using In = Input<DT>;
+    using Raw = typename In::Raw;
+    static_assert(In::kBytes == 2, "16-bit inputs");
+    constexpr int kUnitBytes = 64 * In::kBytes;
+    extern __shared__ uint4 stash_all[];
+    allow_dependent_launch();
+    __shared__ float s_max[kWarpsPerBlock];
+    __shared__ float s_ts;
+    const int lane = threadIdx.x, warp = threadIdx.y;
+    uint4* stash = stash_all + (size_t)warp * per_warp * 32 + lane;   // [unit of the range][lane]
+    const long long pos = ((long long)blockIdx.x * kWarpsPerBlock + warp) * per_warp;
+    const long long end = min(total_units, pos + per_warp);
+    const int sub = lane & 7;
+    grid_dependency_wait();
+    // phase 1: park the range in shared memory, eight loads in flight per lane, and take its maximum
+    float m = 0.0f;
+    {
+        long long p = pos;
+        int j = 0;
+        while (p < end) {
+            const int gi = (int)(p / a.sf_cbg);
+            const int u0 = (int)(p - (long long)gi * a.sf_cbg);
+            const int u1 = (int)min((long long)a.sf_cbg, (long long)u0 + (end - p));
+            const int group = a.row_groups - 1 - gi;
+            const int r = (group >> 5) * 128 + (group & 31) + 32 * (lane >> 3);
+            const char* src = (const char*)a.x + ((int64_t)r * a.cols + u0 * 64 + sub * 8) * In::kBytes;
+            int n = u1 - u0;
+            while (n > 0) {
+                Raw v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n) v[i] = In::load_vec(src + i * kUnitBytes);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n) {
+                        stash[(j + i) * 32] = v[i].v;
+                        m = fmaxf(m, raw_amax<DT>(v[i]));
+                    }
+                src += 8 * kUnitBytes;
+                j += n < 8 ? n : 8;
+                n -= 8;
+            }
+            p += u1 - u0;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) s_max[warp] = m;
+    __syncthreads();
+    if (warp == 0 && lane == 0) {
+        float bm = s_max[0];
+#pragma unroll
+        for (int w = 1; w < kWarpsPerBlock; ++w) bm = fmaxf(bm, s_max[w]);
+        s_ts = grid_meet<DT>(sync, bm, expected_blocks, wait_cycles, scale_out);
+    }
+    __syncthreads();
+    const float ts = s_ts;
+    if (ts < 0.0f || pos >= end) return;
+    // phase 2: quantize the parked range (each lane reads back only what it parked itself)
+    LaneCtx c;
+    c.sub = sub;
+    c.odd = sub & 1;
+    c.ts = ts;
+    c.ts_in_range = ts >= 0x1p-60f && ts <= 0x1p60f;
+    c.rcp_ts = c.ts_in_range ? __frcp_rn(ts) : 0.0f;
+    c.row_in = c.row_out = true;
+    c.hi_first = a.hi_first != 0;
+    c.cols = a.cols;
+    c.pcol = a.pcol;
+    const int x_unit = c.odd ? 1 : 0, y_unit = 1 - x_unit;
+    long long p = pos;
+    int j = 0;
+    while (p < end) {
+        const int gi = (int)(p / a.sf_cbg);
+        const int u0 = (int)(p - (long long)gi * a.sf_cbg);
+        const int u1 = (int)min((long long)a.sf_cbg, (long long)u0 + (end - p));
+        const int group = a.row_groups - 1 - gi;
+        const int band = group >> 5, d3 = group & 31, d4 = lane >> 3;
+        const int r = band * 128 + d3 + 32 * d4;
+        uint8_t* q_row = a.q + (int64_t)r * (a.pcol >> 1) + sub * 4;
+        uint8_t* sf_row = a.sf + (((int64_t)band * a.sf_cbg) * 32 + d3) * 16 + d4 * 4 + (int64_t)(sub & 1) * 512;
+        for (int u = u0; u < u1; u += 2, j += 2) {
+            Raw raw_x, raw_y;
+            raw_x.v = stash[(j + x_unit) * 32];
+            raw_y.v = stash[(j + y_unit) * 32];
+            uint32_t wx, wy, s8;
+            if (c.hi_first) quantize_pair_xy<DT, true>(c, raw_x, raw_y, wx, wy, s8);
+            else quantize_pair_xy<DT, false>(c, raw_x, raw_y, wx, wy, s8);
+            *reinterpret_cast<uint32_t*>(q_row + (u + x_unit) * 32) = wx;
+            *reinterpret_cast<uint32_t*>(q_row + (u + y_unit) * 32) = wy;
+            const uint32_t sfw = gather_scale_word(s8, sub);
+            if (sub < 2) *reinterpret_cast<uint32_t*>(sf_row + (int64_t)u * 512) = sfw;
+        }
+        p += u1 - u0;
+    }
+}
+
+constexpr int kDynamicSmemMaxUnits = 18;   // units per warp the shared-memory variant can park (72 KB per block)
 
 // Resident blocks of the dynamic kernel per SM (cached per device and dtype); never more than kBlocksPerSM.
 template <int DT>
@@ -453,6 +567,26 @@ int dynamic_blocks_per_sm(int* out) {
     return CK_B200_OK;
 }
 
+// Opt the shared-memory variant in to 72 KB per block, once per device and dtype.
+template <int DT>
+int dynamic_smem_ready() {
+    static std::mutex mu;
+    static int cache[64] = {0};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == 0) {
+        constexpr int kBytes = kWarpsPerBlock * kDynamicSmemMaxUnits * 512;
+        CKB_CUDA_OK(cudaFuncSetAttribute(quantize_nvfp4_dynamic_smem_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+        int n = 0;
+        CKB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_nvfp4_dynamic_smem_kernel<DT>,
+                                                                  kWarpsPerBlock * 32, kBytes));
+        cache[dev] = n >= kBlocksPerSM ? 1 : -1;
+    }
+    return cache[dev] > 0 ? CK_B200_OK : -1;   // -1: not an error, the caller takes the other variant
+}
+
 template <int DT>
 int launch_quantize_dynamic(QuantArgs a, float* scale_out, void* sync, int sms, cudaStream_t stream) {
     int per_sm = 0;
@@ -467,9 +601,27 @@ int launch_quantize_dynamic(QuantArgs a, float* scale_out, void* sync, int sms, 
     // test hook: expect arrivals that never come and give up after about 0.1 s instead of 1 s
     const int extra = g_quant_sync_test.load();
     const long long wait_cycles = extra > 0 ? 200000000ll : 2000000000ll;
-    const cudaError_t err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_dynamic_kernel<DT, 2>, dim3(blocks),
-                                             dim3(32, kWarpsPerBlock), 0, stream, a, scale_out, (DynamicSync*)sync, per_warp,
-                                             total, blocks + (unsigned)(extra > 0 ? extra : 0), wait_cycles);
+    const unsigned expected = blocks + (unsigned)(extra > 0 ? extra : 0);
+    cudaError_t err = cudaSuccess;
+    bool launched = false;
+    if constexpr (DT != CK_B200_DTYPE_F32) {
+        // small enough to stay on chip between the phases, and no padding anywhere
+        if (g_dynamic_smem.load() && per_sm == kBlocksPerSM && per_warp <= kDynamicSmemMaxUnits && a.rows % 128 == 0 &&
+            a.cols % 128 == 0 && a.rows == a.prow && a.cols == a.pcol) {
+            const int ready = dynamic_smem_ready<DT>();
+            if (ready > 0) return ready;
+            if (ready == CK_B200_OK) {
+                err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_dynamic_smem_kernel<DT>, dim3(blocks),
+                                       dim3(32, kWarpsPerBlock), (size_t)kWarpsPerBlock * per_warp * 512, stream, a, scale_out,
+                                       (DynamicSync*)sync, per_warp, total, expected, wait_cycles);
+                launched = true;
+            }
+        }
+    }
+    if (!launched)
+        err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_dynamic_kernel<DT, 2>, dim3(blocks),
+                               dim3(32, kWarpsPerBlock), 0, stream, a, scale_out, (DynamicSync*)sync, per_warp, total,
+                               expected, wait_cycles);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
     return CK_B200_OK;

@@ -208,8 +208,9 @@ int ck_b200_dynamic_scale_nvfp4(const void* x_dev, int x_dtype, int64_t numel, f
  * ck.quantize_nvfp4(x, scale)).  Same outputs, bit for bit, as ck_b200_dynamic_scale_nvfp4 followed by
  * ck_b200_quantize_nvfp4; scale_out_dev receives the float32 scale (the GEMM's tensor_scale_a).
  * While x fits the L2 (CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB, default 120) this is ONE kernel launch: every warp takes the
- * maximum over the part of x it will quantize, the blocks meet at a grid-wide counter, then quantize from L2 - the
- * second read of x from HBM is gone.  Larger or oddly shaped inputs (columns not a multiple of 128, unaligned base)
+ * maximum over the part of x it will quantize, the blocks meet at a grid-wide counter, then quantize from L2 - or,
+ * up to about 32 MB of 16-bit input, from shared memory, where the first pass parked it - the second read of x from
+ * HBM is gone.  Larger or oddly shaped inputs (columns not a multiple of 128, unaligned base)
  * take the separate kernels inside the same call.
  *   sync_dev   16 bytes, 16-byte aligned, zero before the first call; the kernel leaves them zero.  Calls that share
  *              them must be ordered on one stream.  NULL selects the separate kernels.
@@ -256,6 +257,8 @@ int ck_b200_read_device_status(int* status_out);
                                         exist and give up after about 0.1 s (the wait then runs out by design) */
 #define CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB 7 /* largest input, in 10^6 bytes, that ck_b200_quantize_nvfp4_dynamic handles
                                              in one launch (default 120: what stays in the 126 MB L2) */
+#define CK_B200_TUNE_DYNAMIC_SMEM 8 /* non-zero (default): inputs of up to about 32 MB with rows and columns multiples of
+                                     128 stay in shared memory between the two phases of ck_b200_quantize_nvfp4_dynamic */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus

@@ -21,6 +21,14 @@ def ckb():
     return m
 
 
+@pytest.fixture(params=[1, 0], ids=["onchip", "l2"])
+def park(request, ckb):
+    """Both forms of the one-launch kernel: small inputs parked in shared memory between its phases, or re-read from L2."""
+    prev = ckb.set_tuning(8, request.param)
+    yield request.param
+    ckb.set_tuning(8, prev)
+
+
 # (rows, cols, pad_16x)
 SHAPES = [(256, 1024, False), (4608, 3072, False), (4608, 12288, False), (16, 4096, False), (32760, 5120, True),
           (129, 200, True), (48, 64, False), (1000, 1152, True)]
@@ -38,7 +46,7 @@ def expected_launches(rows, cols, pad, dtype):
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s[:2])))
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "f16", "f32"])
-def test_dynamic_quantize_vs_oracle(shape, dtype, ckb, oracle):
+def test_dynamic_quantize_vs_oracle(shape, dtype, ckb, oracle, park):
     rows, cols, pad = shape
     want_launches = expected_launches(rows, cols, pad, dtype)
     if dtype != torch.bfloat16 and rows > 5000:
@@ -61,7 +69,7 @@ def test_dynamic_quantize_vs_oracle(shape, dtype, ckb, oracle):
     assert ckb.read_device_status() == 0
 
 
-def test_dynamic_quantize_repeats_and_graph_replays(ckb):
+def test_dynamic_quantize_repeats_and_graph_replays(ckb, park):
     """The meeting-point counters return to zero after every launch, so back-to-back launches and replays of a
     captured launch on changing data keep giving the separate operators' result."""
     x = seeded_randn((2048, 3072), seed=5).cuda()
