@@ -478,10 +478,16 @@ class StepPlan:
             self.peers.barrier()
             torch.cuda.synchronize()
             ok = 1
-            for x, lin, got in zip(self.xs, self.layers, fused_out):
+            for (name, _, _), x, lin, got in zip(self.wl["linears"], self.xs, self.layers, fused_out):
                 want = lin.gather(lin.local(x))          # NCCL all-gather, row-major [M, N]; own memory only
                 if not torch.equal(got, want):
                     ok = 0
+                    nl = lin.local_rows
+                    per_block = [int((got[:, r * nl:(r + 1) * nl] != want[:, r * nl:(r + 1) * nl]).sum()) for r in range(B.world)]
+                    bad_rows = (got != want).any(dim=1).nonzero().flatten()
+                    print(f"[parity] rank {B.rank} linear {name}: differing elements per rank's column block {per_block}, "
+                          f"{bad_rows.numel()} rows affected, first {bad_rows[:8].tolist()} last {bad_rows[-4:].tolist()}",
+                          file=sys.stderr, flush=True)
             flag = torch.tensor([ok], device=B.dev)
             B.dist.all_reduce(flag, op=B.dist.ReduceOp.MIN)
             all_ok = int(flag.item()) == 1

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "ck_b200_set_tuning",
 )
 
-QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_WORKSPACE_BYTES, QUERY_COMPUTE_CAPABILITY, QUERY_LAUNCHES = range(5)
+QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_WORKSPACE_BYTES, QUERY_COMPUTE_CAPABILITY, QUERY_LAUNCHES, QUERY_LAST_GEMM_SPLITS = range(6)
 TUNE_QUANT_VARIANT, TUNE_GEMM_VARIANT = 0, 1
 
 _lib = None

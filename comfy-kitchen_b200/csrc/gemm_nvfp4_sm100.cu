@@ -54,7 +54,10 @@ constexpr int STAGING_BYTES_PER_WARP = 32 * EPI_COLS * 2;   // 32 rows x 32 sixt
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // about 1.5 s
 
 enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5,
-                WAIT_PEER_BARRIER = 6, WAIT_QUANT_BAND = 7 };
+                WAIT_PEER_BARRIER = 6, WAIT_QUANT_BAND = 7, /* 8: the dynamic quantizer's meeting point */
+                WAIT_EPILOGUE_SYNC = 9 };
+constexpr size_t kSplitHeaderBytes = 4096;   // tile counters in front of the split-K partial sums
+constexpr int kSplitMaxTiles = (int)(kSplitHeaderBytes / sizeof(unsigned));
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -72,8 +75,9 @@ struct GemmArgs {
     int m_tiles, n_tiles;
     int raster_group;     // tiles are walked in groups of this many tile rows (all N tiles of a group before the next)
     int splits;           // split-K: every tile is computed by `splits` work items over k_per_split stages each,
-    int k_per_split;      //          which leave fp32 partial sums in `partial` for splitk_reduce_kernel
-    float* partial;       // [splits, M, N] fp32 scratch (split-K only)
+    int k_per_split;      //          which leave fp32 partial sums in `partial`; the item that finishes a tile last
+    float* partial;       //          adds them up.  [splits, M, N] fp32 scratch (split-K only)
+    unsigned* tile_counters;   // [n_tiles] items that have delivered their partial sums; zero between launches
     int a_box_bytes;      // bytes one TMA load of A delivers per stage in the 1-CTA kernel: the box covers only
                           // 32 or 64 rows when M is that small (the rows above stay unwritten and feed accumulator
                           // rows that are never stored)
@@ -306,6 +310,41 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int tile, int& tm
     tm = m0 + (within - tn * rows);
 }
 
+// Split-K: out[m, n] = out_dtype( alpha * sum_s partial[s, m, n] + bias[n] ) for the BN columns of tile column tn, by
+// the 128 epilogue threads of the item that delivered the tile's last partial sums (t = 0..127).  Four columns per
+// thread and step (N % 8 == 0), partial sums read past the L1 (other SMs wrote them), added in split order.
+template <int BN>
+__device__ __forceinline__ void reduce_split_tile(const GemmArgs& g, int tn, float alpha, int t) {
+    const int n0 = tn * BN;
+    const int quads_per_row = min(BN, g.N - n0) >> 2;
+    const int total = g.M * quads_per_row;
+    const int64_t plane = (int64_t)g.M * g.N;
+    for (int i = t; i < total; i += 128) {
+        const int row = i / quads_per_row;
+        const int col = n0 + 4 * (i - row * quads_per_row);
+        const float* p = g.partial + (int64_t)row * g.N + col;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < g.splits; ++s) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p + s * plane));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float y[4] = {acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha};
+        if (g.bias) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] += bias_at(g.bias, g.bias_dtype, col + j);
+        }
+        const int64_t o = (int64_t)row * g.ld_out + col;
+        if (g.out_dtype == CK_B200_DTYPE_F32) {
+            *reinterpret_cast<float4*>((float*)g.out + o) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+            uint2 w;
+            w.x = pack16(y[0], y[1], g.out_dtype);
+            w.y = pack16(y[2], y[3], g.out_dtype);
+            *reinterpret_cast<uint2*>((uint16_t*)g.out + o) = w;
+        }
+    }
+}
+
 // ---- kernel -----------------------------------------------------------------------------------------
 
 // FMT 0: NVFP4 (packed e2m1, e4m3 scales per 16 elements, 256 elements of K per stage).
@@ -327,8 +366,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint64_t* acc_full_bar = bars + 2 * C::kStages;             // [2] MMA -> epilogue
     uint64_t* acc_empty_bar = acc_full_bar + 2;                 // [2] epilogue -> MMA: accumulator drained
     uint64_t* overlap_bar = acc_empty_bar + 2;                  // [1] epilogue -> MMA: shared columns drained
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(overlap_bar + 1);
+    uint64_t* epi_bar = overlap_bar + 1;                        // [2] split-K: the four epilogue warps meet / learn who is last
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* tile_is_last = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -344,6 +385,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             mbar_init(smem_u32(&acc_empty_bar[s]), 128);
         }
         mbar_init(smem_u32(overlap_bar), 128);
+        mbar_init(smem_u32(&epi_bar[0]), 4);
+        mbar_init(smem_u32(&epi_bar[1]), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -507,7 +550,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // ---------------- epilogue (warps 2..5) ----------------
         const int quad = warp & 3;   // tensor-memory lanes [32*quad, 32*quad+32) are the ones this warp may read
         int acc = 0;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, epi_phase = 0;
         bool ok = true;
         long long wait_acc = 0;
         const long long t_begin = now();
@@ -600,6 +643,33 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             mbar_arrive(smem_u32(&acc_empty_bar[acc]));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
+            if (g.splits > 1) {
+                // Split-K: this item's partial sums are in the scratch.  The four epilogue warps meet, one thread
+                // counts the item in on the tile's counter, and the item that arrives last adds the partial sums of
+                // all of them up (in split order, so the result does not depend on who was last), applies alpha and
+                // bias and writes the output tile.  Both meetings are bounded waits like every other wait here.
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&epi_bar[0]));
+                ok = mbar_wait(smem_u32(&epi_bar[0]), epi_phase, abort_flag, WAIT_EPILOGUE_SYNC);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (warp == 2 && lane == 0) {
+                    const unsigned arrived = atomicAdd(&g.tile_counters[tile], 1u) + 1u;
+                    const bool last = arrived == (unsigned)g.splits;
+                    if (last) g.tile_counters[tile] = 0u;   // every item of the tile is in: zero again for the next launch
+                    *tile_is_last = last ? 1 : 0;
+                    mbar_arrive(smem_u32(&epi_bar[1]));
+                }
+                ok = mbar_wait(smem_u32(&epi_bar[1]), epi_phase, abort_flag, WAIT_EPILOGUE_SYNC);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                epi_phase ^= 1;
+                if (*tile_is_last) {
+                    __threadfence();
+                    reduce_split_tile<BN>(g, tn, alpha, (int)threadIdx.x - 64);
+                }
+            }
         }
         if (g.tma_store && lane == 0) tma_store_wait_all();   // global writes complete before the CTA exits
         if (DBG && blockIdx.x == 0 && threadIdx.x == 64)
@@ -1204,39 +1274,6 @@ __global__ void peer_barrier_kernel(const BarrierArgs b) {
     if (t == 0) *b.epoch = target;
 }
 
-// ---- split-K reduction ----------------------------------------------------------------------------
-
-// out[m,n] = out_dtype( alpha * sum_s partial[s,m,n] + bias[n] ), four columns per thread (N % 8 == 0).
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
-                                                            const float* tsa, const float* tsb, const float* alpha_ptr,
-                                                            const void* bias, int bias_dtype, void* out, int out_dtype) {
-    allow_dependent_launch();
-    const int64_t quads = (int64_t)M * N / 4;
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= quads) return;
-    grid_dependency_wait();
-    const float alpha = alpha_ptr ? __ldg(alpha_ptr) : __fmul_rn(__ldg(tsa), __ldg(tsb));
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < splits; ++s) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (int64_t)s * quads + i);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    float y[4] = {acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha};
-    const int n = (int)((i * 4) % N);
-    if (bias) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) y[j] += bias_at(bias, bias_dtype, n + j);
-    }
-    if (out_dtype == CK_B200_DTYPE_F32) {
-        reinterpret_cast<float4*>(out)[i] = make_float4(y[0], y[1], y[2], y[3]);
-    } else {
-        uint2 o;
-        o.x = pack16(y[0], y[1], out_dtype);
-        o.y = pack16(y[2], y[3], out_dtype);
-        reinterpret_cast<uint2*>(out)[i] = o;
-    }
-}
-
 // ---- host side --------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1270,6 +1307,38 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(CK_B200_ERR_CUDA, "cuTensorMapEncodeTiled (operand) failed with CUresult %d", (int)r);
+    return CK_B200_OK;
+}
+
+// make_operand_map for an operand that stays where it is over many calls (a resident weight): the encoded map is kept
+// in a small per-process table keyed by address, shape and box, so the driver call happens once per weight.  A map
+// only describes memory (base, extents, strides), so a stale entry for a freed and reused address is still a valid
+// description of whatever matrix of that shape now lives there.
+int cached_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_bytes, int box_rows, int box_bytes = BK_BYTES) {
+    struct Entry {
+        const void* ptr;
+        int64_t rows, k_bytes;
+        int box_rows, box_bytes, dev;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 256;
+    static std::mutex mu;
+    static Entry table[kEntries] = {};
+    int dev = 0;
+    CKB_CUDA_OK(cudaGetDevice(&dev));
+    const size_t h = ((reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull >> 40) % kEntries;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        const Entry& e = table[h];
+        if (e.ptr == ptr && e.rows == rows && e.k_bytes == k_bytes && e.box_rows == box_rows && e.box_bytes == box_bytes &&
+            e.dev == dev) {
+            *map = e.map;
+            return CK_B200_OK;
+        }
+    }
+    if (int rc = make_operand_map(map, ptr, rows, k_bytes, box_rows, box_bytes)) return rc;
+    std::lock_guard<std::mutex> lock(mu);
+    table[h] = Entry{ptr, rows, k_bytes, box_rows, box_bytes, dev, *map};
     return CK_B200_OK;
 }
 
@@ -1381,6 +1450,7 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g_last_splits.store(1);
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
     const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(kThreads), kSmemBytes2, stream, ma, mb, msa, msb, mo, g, fq);
@@ -1399,28 +1469,38 @@ int choose_splits(int n_tiles, int k_iters, int sms, int64_t M, int64_t N, size_
     return s < 1 ? 1 : s;
 }
 
+// Scratch of a split-K launch: `counters` (kSplitHeaderBytes, zero between launches) and room for the partial sums.
+struct SplitScratch {
+    unsigned* counters = nullptr;
+    float* partial = nullptr;
+    size_t partial_bytes = 0;
+};
+
 template <int BN, int FMT = 0>
-int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream, float* scratch,
-                size_t scratch_bytes) {
+int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream, SplitScratch scratch) {
     using C = Cfg<BN>;
     auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true, FMT> : gemm_nvfp4_kernel<BN, false, FMT>;
     const int64_t row_bytes = FMT == 1 ? K : K / 2;   // e4m3 bytes or packed e2m1 nibbles
-    // opting in to large dynamic shared memory is per function and per device; doing it on every call is cheap
-    cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (attr_err != cudaSuccess)
-        return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
-                    cudaGetErrorString(attr_err));
+    // opting in to large dynamic shared memory is per function and per device: once
+    {
+        static std::mutex mu;
+        static bool done[2][64] = {};
+        int dev = 0;
+        CKB_CUDA_OK(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !done[g.debug ? 1 : 0][dev]) {
+            cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+            if (attr_err != cudaSuccess)
+                return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
+                            cudaGetErrorString(attr_err));
+            if (dev >= 0 && dev < 64) done[g.debug ? 1 : 0][dev] = true;
+        }
+    }
     CUtensorMap ma, mb, mo;
     const int a_box_rows = g.M <= 32 ? 32 : g.M <= 64 ? 64 : BM;
     g.a_box_bytes = a_box_rows * BK_BYTES;
     if (int rc = make_operand_map(&ma, a, g.M, row_bytes, a_box_rows)) return rc;
-    if (int rc = make_operand_map(&mb, b, g.N, row_bytes, BN)) return rc;
-    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
-    if (g.tma_store) {
-        if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
-    } else {
-        mo = ma;   // not used by the kernel
-    }
+    if (int rc = cached_operand_map(&mb, b, g.N, row_bytes, BN)) return rc;   // the weight: the same matrix call after call
     g.m_tiles = (int)ceil_div64(g.M, BM);
     g.n_tiles = (int)ceil_div64(g.N, BN);
     // as many tile rows per group as keep the group's A rows (with room for B and the output) inside the 126 MB L2
@@ -1431,27 +1511,31 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
-    if (g.m_tiles == 1 && scratch != nullptr) {
-        g.splits = choose_splits(g.n_tiles, g.k_iters, sms, g.M, g.N, scratch_bytes);
+    g.tile_counters = nullptr;
+    if (g.m_tiles == 1 && scratch.partial != nullptr && scratch.counters != nullptr && g.n_tiles <= kSplitMaxTiles) {
+        g.splits = choose_splits(g.n_tiles, g.k_iters, sms, g.M, g.N, scratch.partial_bytes);
         if (g.splits > 1) {
             g.k_per_split = (int)ceil_div64(g.k_iters, g.splits);
             g.splits = (int)ceil_div64(g.k_iters, g.k_per_split);   // no empty work items
-            g.partial = scratch;
+        }
+        if (g.splits > 1) {
+            g.partial = scratch.partial;
+            g.tile_counters = scratch.counters;
         }
     }
+    // split-K items write fp32 partial sums and the last item of a tile stores the output itself: no output map
+    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32 && g.splits == 1) ? 1 : 0;
+    if (g.tma_store) {
+        if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
+    } else {
+        mo = ma;   // not used by the kernel
+    }
+    g_last_splits.store(g.splits);
     const int64_t items = (int64_t)g.m_tiles * g.n_tiles * g.splits;
     const unsigned grid = (unsigned)(items < sms ? items : sms);
     const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
-    if (g.splits > 1) {
-        const int64_t quads = (int64_t)g.M * g.N / 4;
-        const cudaError_t err2 = launch_dependent(kLaunchFamilyGemm, splitk_reduce_kernel, dim3((unsigned)ceil_div64(quads, 256)), dim3(256), 0,
-                                                  stream, g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias,
-                                                  g.bias_dtype, g.out, g.out_dtype);
-        g_launches.fetch_add(1);
-        CKB_CUDA_OK(err2);
-    }
     return CK_B200_OK;
 }
 
@@ -1471,7 +1555,7 @@ struct GatherSpec {
 int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
                    const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
                    const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N,
-                   int64_t K, void* workspace_dev, size_t workspace_bytes, void* stream,
+                   int64_t K, SplitScratch scratch, void* stream,
                    const GatherSpec* gather = nullptr, const FusedQuant* fused = nullptr, int fused_dtype = -1) {
     int sms = 0;
     if (int rc = check_device(&sms)) return rc;
@@ -1513,6 +1597,7 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g.tile_counters = nullptr;
     g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
@@ -1525,9 +1610,8 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
     if (variant == 0) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
-    if (workspace_dev && ((uintptr_t)workspace_dev & 15))
+    if (((uintptr_t)scratch.partial & 15) || ((uintptr_t)scratch.counters & 15))
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
-    float* scratch = (float*)workspace_dev;
     if (gather) {
         if (out_dtype == CK_B200_DTYPE_F32 || M <= 128 || N <= 128)
             return fail(CK_B200_ERR_INVALID_ARGUMENT,
@@ -1548,9 +1632,20 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     }
     if (variant == 4 && M > 128) return launch_gemm_pair<64>(a_dev, b_dev, g, K, s);
     if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
-    if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch);
     // one tile row: 128-column tiles give the most work items, and split-K (with scratch) fills the remaining SMs
-    return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch);
+}
+
+// A caller's workspace as split-K scratch: the tile counters in its first kSplitHeaderBytes, partial sums behind them.
+SplitScratch scratch_from_workspace(void* workspace_dev, size_t workspace_bytes) {
+    SplitScratch sc;
+    if (workspace_dev && workspace_bytes > kSplitHeaderBytes + (1u << 16)) {
+        sc.counters = (unsigned*)workspace_dev;
+        sc.partial = (float*)((char*)workspace_dev + kSplitHeaderBytes);
+        sc.partial_bytes = workspace_bytes - kSplitHeaderBytes;
+    }
+    return sc;
 }
 }  // namespace
 
@@ -1560,8 +1655,28 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
                                        void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* workspace_dev,
                                        size_t workspace_bytes, void* stream) {
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
-                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, workspace_dev, workspace_bytes, stream);
+                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K,
+                          scratch_from_workspace(workspace_dev, workspace_bytes), stream);
 }
+
+namespace ckb {
+// scaled_mm_nvfp4 with the split-K scratch given as its two parts (the whole-linear entry point keeps the counters at
+// a fixed place of its workspace and the partial sums behind the quantized activation).
+int scaled_mm_nvfp4_split(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
+                          const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const void* bias_dev_or_null,
+                          int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* counters_dev,
+                          void* partial_dev, size_t partial_bytes, void* stream) {
+    SplitScratch sc;
+    if (counters_dev && partial_dev && partial_bytes >= (1u << 16)) {
+        sc.counters = (unsigned*)counters_dev;
+        sc.partial = (float*)partial_dev;
+        sc.partial_bytes = partial_bytes;
+    }
+    return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, nullptr, bias_dev_or_null,
+                          bias_dtype, out_dev, out_dtype, M, N, K, sc, stream);
+}
+size_t split_header_bytes() { return kSplitHeaderBytes; }
+}  // namespace ckb
 
 
 // ---- GEMM that quantizes its own activations -------------------------------------------------------------
@@ -1605,7 +1720,7 @@ int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, co
     fq.sync = (FusedQuantSync*)sync_dev;
     fq.bands = a.row_groups / 32;
     return scaled_mm_impl(qx_dev, sfx_dev, w_q_dev, w_sf_dev, ts_x_dev, w_scale_dev, nullptr, bias_dev_or_null,
-                          bias_dtype, out_dev, out_dtype, M, N, K, nullptr, 0, stream, nullptr, &fq, x_dtype);
+                          bias_dtype, out_dev, out_dtype, M, N, K, SplitScratch{}, stream, nullptr, &fq, x_dtype);
 }
 }  // namespace ckb
 
@@ -1634,7 +1749,7 @@ extern "C" int ck_b200_scaled_mm_nvfp4_all_gather(const void* a_dev, const void*
     }
     void* own = (uint8_t*)out_ptrs[rank] + block_bytes;
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
-                          bias_dev_or_null, bias_dtype, own, out_dtype, M, N_local, K, nullptr, 0, stream, &spec);
+                          bias_dev_or_null, bias_dtype, own, out_dtype, M, N_local, K, SplitScratch{}, stream, &spec);
 }
 
 // ---- barrier between the ranks of one node ------------------------------------------------------------
@@ -1721,6 +1836,7 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g.tile_counters = nullptr;
     g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
@@ -1729,26 +1845,28 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
     for (int p = 0; p < 7; ++p) g.peer_out[p] = nullptr;
     g.debug = g_gemm_debug.load();
     cudaStream_t s = (cudaStream_t)stream;
-    float* scratch = (float*)workspace_dev;
+    const SplitScratch scratch = scratch_from_workspace(workspace_dev, workspace_bytes);
     // the same choice of tiles as the NVFP4 entry point; variants 1 and 2 force the 1-CTA kernels
     int variant = g_gemm_variant.load();
     if (variant == 0 || variant > 3) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     if (variant == 3 && M > 128) return launch_gemm_pair<128, 1>(a_dev, b_dev, g, K, s);
-    if (variant == 2 && M > 128) return launch_gemm<256, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
-    return launch_gemm<128, 1>(a_dev, b_dev, g, K, sms, s, scratch, workspace_bytes);
+    if (variant == 2 && M > 128) return launch_gemm<256, 1>(a_dev, b_dev, g, K, sms, s, scratch);
+    return launch_gemm<128, 1>(a_dev, b_dev, g, K, sms, s, scratch);
 }
 
 // ---- entry point with built-in scratch --------------------------------------------------------------
 
 namespace {
-constexpr size_t kStaticScratchBytes = 8u << 20;
-// Split-K partial sums for callers that cannot hand over device memory of their own.  Lives in the library image:
-// every device that loads the library holds these 8 MiB until the process exits.
+constexpr size_t kStaticPartialBytes = 8u << 20;
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kSplitHeaderBytes;
+// Split-K scratch for callers that cannot hand over device memory of their own: the tile counters (4 KiB, zero when
+// the library is loaded and left zero by every launch) followed by 8 MiB for partial sums.  Lives in the library
+// image: every device that loads the library holds it until the process exits.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // Device address of g_static_scratch on the current device, looked up once per device.  In host code the array's
 // name is only a handle for the runtime, not a device pointer, so it is never passed to a kernel directly.
-int static_scratch_address(float** out) {
+int static_scratch_address(unsigned char** out) {
     static std::mutex mu;
     static void* cache[64] = {nullptr};
     int dev = 0;
@@ -1762,7 +1880,7 @@ int static_scratch_address(float** out) {
             return fail(CK_B200_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
         cache[dev] = p;
     }
-    *out = reinterpret_cast<float*>(cache[dev]);
+    *out = reinterpret_cast<unsigned char*>(cache[dev]);
     return CK_B200_OK;
 }
 }  // namespace
@@ -1776,15 +1894,16 @@ extern "C" int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const v
         return fail(CK_B200_ERR_INVALID_ARGUMENT,
                     "scaled_mm_nvfp4_static_scratch: M = %lld is beyond the limit of 128 rows (larger problems need no "
                     "scratch: use ck_b200_scaled_mm_nvfp4)", (long long)M);
-    if (M > 0 && N > 0 && (size_t)M * (size_t)N * 4 * 2 > kStaticScratchBytes)
+    if (M > 0 && N > 0 && (size_t)M * (size_t)N * 4 * 2 > kStaticPartialBytes)
         return fail(CK_B200_ERR_INVALID_ARGUMENT,
                     "scaled_mm_nvfp4_static_scratch: M * N = %lld is beyond the limit of %lld outputs (two fp32 partial "
                     "sums per output must fit the %lld-byte built-in scratch)",
-                    (long long)(M * N), (long long)(kStaticScratchBytes / 8), (long long)kStaticScratchBytes);
-    float* scratch = nullptr;
+                    (long long)(M * N), (long long)(kStaticPartialBytes / 8), (long long)kStaticPartialBytes);
+    unsigned char* scratch = nullptr;
     if (int rc = static_scratch_address(&scratch)) return rc;
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
-                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K, scratch, kStaticScratchBytes, stream);
+                          bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K,
+                          scratch_from_workspace(scratch, kStaticScratchBytes), stream);
 }
 
 extern "C" int ck_b200_read_device_status(int* status_out) {

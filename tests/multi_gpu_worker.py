@@ -21,8 +21,11 @@ def main() -> int:
     dist.init_process_group("nccl", device_id=dev)
     ok = True
     peers = ckb.PeerGroup(dev)
-    M = 1024
-    for (K, N, seed) in [(1024, 2048, 1), (3072, 3072, 2)]:
+    # small shapes, then the four linears of the Flux-class block at its full M (the shapes the benchmark times)
+    for (M, K, N, seed) in [(1024, 1024, 2048, 1), (1024, 3072, 3072, 2), (4608, 3072, 9216, 3), (4608, 3072, 3072, 4),
+                            (4608, 3072, 12288, 5), (4608, 12288, 3072, 6)]:
+        if (N // world) % 8 or N // world <= 128:
+            continue
         x = replicated_from_seed((M, K), seed, 1.0, torch.bfloat16, dev)
         w = replicated_from_seed((N, K), seed + 100, 0.02, torch.bfloat16, dev)
         lin = ckb.ShardedNVFP4Linear(w, None, input_scale=ckb.dynamic_scale_nvfp4(x))
@@ -36,7 +39,10 @@ def main() -> int:
             same = torch.equal(got, want)
             ok = ok and same
             if not same:
-                print(f"rank {rank}: K={K} N={N} iteration {it}: fused result differs", flush=True)
+                nl = N // world
+                blocks = [int((got[:, r * nl:(r + 1) * nl] != want[:, r * nl:(r + 1) * nl]).sum()) for r in range(world)]
+                print(f"rank {rank}: M={M} K={K} N={N} iteration {it}: fused result differs; differing elements per "
+                      f"rank's column block {blocks}", flush=True)
     status = ckb.read_device_status()
     ok = ok and status == 0
     flag = torch.tensor([1 if ok else 0], device=dev)

@@ -36,7 +36,7 @@ def test_host_only_entry_points(ckb):
     """Entry points that need no GPU: error text, tuning switches, ABI version."""
     from comfy_kitchen_b200 import _lib
     L = _lib.load()
-    assert L.ck_b200_query(_lib.QUERY_ABI_VERSION) == 1
+    assert L.ck_b200_query(_lib.QUERY_ABI_VERSION) == 2
     assert L.ck_b200_query(12345) == -1
     prev = L.ck_b200_set_tuning(_lib.TUNE_QUANT_VARIANT, 0)
     assert L.ck_b200_set_tuning(_lib.TUNE_QUANT_VARIANT, prev) == 0

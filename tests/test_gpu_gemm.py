@@ -75,7 +75,7 @@ def test_gemm_golden(name, golden, ckb, variant):
 
 
 SMALL = [(256, 1024, 1024), (128, 128, 256), (16, 8, 32), (100, 200, 96), (129, 136, 320), (384, 264, 1024),
-         (1, 4096, 4096), (16, 10240, 4096), (64, 4096, 10240), (512, 1024, 2048), (300, 520, 2080)]
+         (1, 4096, 4096), (16, 10240, 4096), (64, 4096, 10240), (128, 4096, 4096), (512, 1024, 2048), (300, 520, 2080)]
 
 
 @pytest.mark.parametrize("mnk", SMALL, ids=lambda s: "x".join(map(str, s)))
@@ -158,6 +158,43 @@ def test_gemm_full_size_vs_cublaslt(mnk, ckb, variant):
     # linearity: alpha = 2 * tsx * tsw doubles the output exactly (power-of-two scaling commutes with rounding)
     y2 = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, alpha=(2.0 * tsx * tsw))
     assert torch.equal(y2.float(), 2.0 * y.float())
+
+
+@pytest.mark.parametrize("mnk", [(1, 4096, 4096), (16, 10240, 4096), (64, 4096, 10240), (128, 2048, 8192)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_split_k_repeats_and_graph_replays(mnk, ckb):
+    """Small M is cut along K and the work item that finishes a tile last adds the partial sums up inside the kernel;
+    the per-tile counters return to zero, so repeated calls and replays of a captured call on changing operands keep
+    giving the bits of the first call (summation order is fixed, whichever item is last)."""
+    from comfy_kitchen_b200 import _lib
+    M, N, K = mnk
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=7 * M + N)
+    first = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+    assert _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS) > 1, "this shape is expected to take split-K"
+    for _ in range(4):
+        assert torch.equal(ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw), first)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)      # this stream's workspace exists before the capture
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream), torch.cuda.graph(graph):
+        y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+    for i in range(3):
+        with torch.cuda.stream(stream):
+            graph.replay()
+        stream.synchronize()
+        assert torch.equal(y, first)
+    # other operands through the same captured call
+    x2, w2, qx2, sfx2, tsx2, qw2, sfw2, tsw2 = quantized_operands(ckb, M, N, K, seed=11 * M + N)
+    want = ckb.scaled_mm_nvfp4(qx2, qw2, tsx2, tsw2, sfx2, sfw2)
+    for dst, src in ((qx, qx2), (sfx, sfx2), (tsx, tsx2), (qw, qw2), (sfw, sfw2), (tsw, tsw2)):
+        dst.copy_(src)
+    with torch.cuda.stream(stream):
+        graph.replay()
+    stream.synchronize()
+    assert torch.equal(y, want)
+    assert ckb.read_device_status() == 0
 
 
 def test_gemm_rejects_bad_arguments(ckb):

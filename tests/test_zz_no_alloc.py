@@ -54,14 +54,17 @@ def test_static_scratch_entry_point_matches_regular_one():
         n0 = ckb.launches()
         expected = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias, out_dtype=dt)
         regular_launches = ckb.launches() - n0
+        regular_splits = L.ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
         out = torch.full((M, N), float("nan"), dtype=dt, device="cuda")
         n0 = ckb.launches()
         rc = L.ck_b200_scaled_mm_nvfp4_static_scratch(
             qx.data_ptr(), sfx.data_ptr(), qw.data_ptr(), sfw.data_ptr(), tsx.data_ptr(), tsw.data_ptr(), None,
             bias.data_ptr(), 2, out.data_ptr(), code, M, N, K, stream)
         assert rc == 0, _lib.last_error()
-        # the split-K path ran (partial sums through the scratch, then the reduction), as in the regular call
-        assert ckb.launches() - n0 == regular_launches == 2
+        # the split-K path ran (partial sums through the built-in scratch, summed inside the same kernel), cut into
+        # as many pieces as the regular call's
+        assert ckb.launches() - n0 == regular_launches == 1
+        assert L.ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS) == regular_splits > 1
         torch.cuda.synchronize()
         assert torch.isfinite(out.float()).all()
         assert torch.equal(out, expected), "static-scratch result differs from the regular entry point's"
