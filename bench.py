@@ -781,14 +781,16 @@ def wan_record(B: Bench, args):
             plan.step()
         B.barrier()
         parity = plan.check_parity() if B.distributed else None
-        replay, launches = B.graphed(plan.step, use_graph=plan.use_graph)
+        overlap = plan.use_graph and not args.serial
+        replay, launches = B.graphed(plan.step_overlapped if overlap else plan.step, use_graph=plan.use_graph)
         for _ in range(2):
             replay()
         ms = B.timed(replay, steps) / steps
         fl = flops_per_step(wl)
         rec = {"workload": wl["name"], "M": wl["M"], "linears": [list(l) for l in wl["linears"]], "steps": steps,
                "ms_per_step": ms, "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": B.world,
-               "mode": plan.mode_text(), "launch": "one CUDA graph per step" if plan.use_graph else "eager launches",
+               "mode": plan.mode_text(), "launch": ("one CUDA graph per step" + (", quantizers on a second branch" if overlap else ""))
+               if plan.use_graph else "eager launches",
                "gpu_launches_per_step": launches, "parity": parity,
                "data": "synthetic, generated on the device from a seeded generator"}
         if plan.fused:
@@ -848,7 +850,13 @@ def run_ours(args, wl):
         sys.exit(3)
 
     # ---- the timed region: exactly K steps ----
-    replay_step, launches_per_step = B.graphed(lambda: plan.step(one_call=one_call), use_graph=plan.use_graph)
+    # The step's four linears are independent work items (each has its own activation), so the step is one CUDA graph
+    # with two branches: the quantizers on one, the GEMMs on the other, and the quantizer of linear i+1 runs beside the
+    # GEMM of linear i (on several GPUs: beside its stores to the peers, so the link does not idle).  The same at every
+    # GPU count.  `serial_chain` below is the same work with the eight kernels one after the other.
+    overlap = plan.use_graph and not one_call and not args.serial
+    step_fn = plan.step_overlapped if overlap else (lambda: plan.step(one_call=one_call))
+    replay_step, launches_per_step = B.graphed(step_fn, use_graph=plan.use_graph)
     for _ in range(warm):
         replay_step()
     ms = B.timed(replay_step, args.steps)
@@ -857,21 +865,19 @@ def run_ours(args, wl):
     fl = flops_per_step(wl)
     value = fl * args.steps / (ms * 1e-3) / 1e12
 
-    # ---- the same K steps with the quantizers on a second branch of the graph (independent linears overlap) ----
-    overlapped = None
-    if plan.use_graph and not one_call:
-        replay_o, n_o = B.graphed(plan.step_overlapped)
+    serial_chain = None
+    if overlap:
+        replay_s, n_s = B.graphed(lambda: plan.step(one_call=one_call), use_graph=plan.use_graph)
         for _ in range(warm):
-            replay_o()
-        ms_o = B.timed(replay_o, args.steps)
-        overlapped = {"ms_per_step": ms_o / args.steps, "value": fl * args.steps / (ms_o * 1e-3) / 1e12,
-                      "gpu_launches_per_step": n_o,
-                      "what": "one CUDA graph with two branches: the quantizer of linear i+1 runs beside the GEMM "
-                              "of linear i (the step's linears are independent work items); `value` above is the "
-                              "serial chain"}
+            replay_s()
+        ms_s = B.timed(replay_s, args.steps)
+        serial_chain = {"ms_per_step": ms_s / args.steps, "value": fl * args.steps / (ms_s * 1e-3) / 1e12,
+                        "gpu_launches_per_step": n_s,
+                        "what": "the same eight kernels in one chain (quantize, GEMM, quantize, GEMM, ...): what a block "
+                                "whose linears depend on one another can do"}
         if fused:
             out_bytes = sum(M * lin.local_rows * 2 for lin in layers) * (world - 1)
-            overlapped["nvlink_achieved_gbs"] = out_bytes / (ms_o / args.steps * 1e-3) / 1e9
+            serial_chain["nvlink_achieved_gbs"] = out_bytes / (ms_s / args.steps * 1e-3) / 1e9
 
     # ---- the step with per-call (dynamic) activation scales: what the layer does when a checkpoint has no input_scale
     dynamic = None
@@ -881,7 +887,8 @@ def run_ours(args, wl):
             replay_d()
         ms_d = B.timed(replay_d, args.steps)
         dynamic = {"ms_per_step": ms_d / args.steps, "value": fl * args.steps / (ms_d * 1e-3) / 1e12,
-                   "gpu_launches_per_step": n_d, "slowdown_vs_static": ms_d / ms - 1.0,
+                   "gpu_launches_per_step": n_d,
+                   "slowdown_vs_static_serial_chain": (ms_d / args.steps) / (serial_chain["ms_per_step"] if serial_chain else ms / args.steps) - 1.0,
                    "what": "input_scale = None: amax(|x|)/(448*6) in the activation's dtype derived on the device in "
                            "front of every quantizer (comfy_kitchen/tensor/nvfp4.py:66-71), no host round trip"}
 
@@ -1141,9 +1148,12 @@ def run_ours(args, wl):
                     "launch": "one CUDA graph per step" if plan.use_graph else "eager launches",
                     "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
                                "(ck_b200_linear_nvfp4)") if one_call and not distributed else
+                              ("quantize_nvfp4 kernel and scaled_mm_nvfp4 kernel per linear; the four linears are independent "
+                               "work items, so the quantizer of linear i+1 runs beside the GEMM of linear i (two branches of "
+                               "one CUDA graph); serial_chain gives the same kernels one after the other") if overlap else
                               "quantize_nvfp4 kernel, then scaled_mm_nvfp4 kernel, the four linears one after the other"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "parity": parity, "sustained": sustained, "overlapped": overlapped, "dynamic_scale_step": dynamic,
+            "parity": parity, "sustained": sustained, "serial_chain": serial_chain, "dynamic_scale_step": dynamic,
             "fp4_ceiling": ceiling, "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
             "quantize_sweep": sweep, "quantize_comparators": comparators, "small_m_sweep": small_m, "mxfp8": mxfp8,
@@ -1168,8 +1178,11 @@ def main():
                     help="skip the single-GPU extras: sustained run, FP4 ceiling, quantizer sweep and comparators, "
                          "small-M sweep, MXFP8")
     ap.add_argument("--no-wan", action="store_true", help="skip the short record of the Wan-class workload")
+    ap.add_argument("--serial", action="store_true",
+                    help="time the eight kernels of a step as one chain instead of overlapping each quantizer with the "
+                         "previous linear's GEMM")
     ap.add_argument("--sustained-seconds", type=float, default=3.0)
-    ap.add_argument("--peer-map-limit-gib", type=int, default=4,
+    ap.add_argument("--peer-map-limit-gib", type=int, default=64,
                     help="N > 1: above this many GiB of peer-mapped output matrices per rank the NCCL all-gather is used")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic stream serialisation")

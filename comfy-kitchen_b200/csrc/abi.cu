@@ -157,7 +157,7 @@ int ck_b200_peer_free(void* ptr) {
 namespace {
 struct LinearPlan {
     int64_t prow;          // activation rows after padding to 16
-    size_t scale_off, dyn_sync_off, q_off, sf_off, sync_off, split_hdr_off, end;   // byte offsets inside the workspace
+    size_t scale_off, dyn_sync_off, q_off, sf_off, sync_off, end;   // byte offsets inside the workspace
 };
 LinearPlan plan_linear(int64_t M, int64_t K) {
     LinearPlan p;
@@ -167,9 +167,7 @@ LinearPlan plan_linear(int64_t M, int64_t K) {
     // the sync area of the fused kernel sits at the same place for every shape, so that nothing but that kernel
     // ever writes there when linears of different shapes share one workspace
     p.sync_off = 256;
-    // counters of the split-K GEMM (M <= 128), also at a fixed place and zero between calls
-    p.split_hdr_off = p.sync_off + ckb::fused_sync_bytes();
-    p.q_off = p.split_hdr_off + ckb::split_header_bytes();
+    p.q_off = p.sync_off + ckb::fused_sync_bytes();
     p.sf_off = p.q_off + (size_t)ckb::round_up64(p.prow * (K / 2), 256);
     p.end = p.sf_off + (size_t)ckb::round_up64(ckb::round_up64(p.prow, 128) * ckb::round_up64(K / 16, 4), 256);
     return p;
@@ -219,11 +217,11 @@ int ck_b200_linear_nvfp4(const void* x_dev, int x_dtype, int64_t M, int64_t K, c
     } else if (int rc = ck_b200_quantize_nvfp4(x_dev, x_dtype, ts_x, qx, sfx, M, K, /*pad_16x=*/1, /*hi_first=*/1, stream)) {
         return rc;
     }
-    // what is left of the workspace holds the split-K partial sums of small-M problems
+    // what is left of the workspace serves the split-K reduction of small-M problems
     const size_t rest = workspace_bytes - p.end;
-    return ckb::scaled_mm_nvfp4_split(qx, sfx, w_q_dev, w_sf_dev, ts_x, w_scale_dev, bias_dev_or_null, bias_dtype, out_dev,
-                                      out_dtype, M, N, K, ws + p.split_hdr_off, rest >= (1u << 20) ? ws + p.end : nullptr,
-                                      rest >= (1u << 20) ? rest : 0, stream);
+    return ck_b200_scaled_mm_nvfp4(qx, sfx, w_q_dev, w_sf_dev, ts_x, w_scale_dev, nullptr, bias_dev_or_null, bias_dtype,
+                                   out_dev, out_dtype, M, N, K, rest >= (1u << 20) ? ws + p.end : nullptr,
+                                   rest >= (1u << 20) ? rest : 0, stream);
 }
 
 }  // extern "C"

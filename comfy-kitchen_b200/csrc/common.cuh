@@ -45,13 +45,6 @@ int fused_linear_launch(const void* x_dev, int x_dtype, int64_t M, int64_t K, co
                         const float* w_scale_dev, int64_t N, const void* bias_dev_or_null, int bias_dtype, void* out_dev,
                         int out_dtype, void* stream);
 
-// scaled_mm_nvfp4 with the split-K scratch given as its two parts, and the size of the counter area.
-int scaled_mm_nvfp4_split(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
-                          const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const void* bias_dev_or_null,
-                          int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* counters_dev,
-                          void* partial_dev, size_t partial_bytes, void* stream);
-size_t split_header_bytes();
-
 #define CKB_CUDA_OK(expr)                                                                              \
     do {                                                                                               \
         cudaError_t e__ = (expr);                                                                      \

@@ -54,10 +54,7 @@ constexpr int STAGING_BYTES_PER_WARP = 32 * EPI_COLS * 2;   // 32 rows x 32 sixt
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;   // about 1.5 s
 
 enum WaitCode { WAIT_STAGE_EMPTY = 1, WAIT_STAGE_FULL = 2, WAIT_ACC_EMPTY = 3, WAIT_ACC_FULL = 4, WAIT_OVERLAP = 5,
-                WAIT_PEER_BARRIER = 6, WAIT_QUANT_BAND = 7, /* 8: the dynamic quantizer's meeting point */
-                WAIT_EPILOGUE_SYNC = 9 };
-constexpr size_t kSplitHeaderBytes = 4096;   // tile counters in front of the split-K partial sums
-constexpr int kSplitMaxTiles = (int)(kSplitHeaderBytes / sizeof(unsigned));
+                WAIT_PEER_BARRIER = 6, WAIT_QUANT_BAND = 7 /* 8: the dynamic quantizer's meeting point */ };
 
 struct GemmArgs {
     const uint8_t* sfa;
@@ -75,9 +72,8 @@ struct GemmArgs {
     int m_tiles, n_tiles;
     int raster_group;     // tiles are walked in groups of this many tile rows (all N tiles of a group before the next)
     int splits;           // split-K: every tile is computed by `splits` work items over k_per_split stages each,
-    int k_per_split;      //          which leave fp32 partial sums in `partial`; the item that finishes a tile last
-    float* partial;       //          adds them up.  [splits, M, N] fp32 scratch (split-K only)
-    unsigned* tile_counters;   // [n_tiles] items that have delivered their partial sums; zero between launches
+    int k_per_split;      //          which leave fp32 partial sums in `partial` for splitk_reduce_kernel
+    float* partial;       // [splits, M, N] fp32 scratch (split-K only)
     int a_box_bytes;      // bytes one TMA load of A delivers per stage in the 1-CTA kernel: the box covers only
                           // 32 or 64 rows when M is that small (the rows above stay unwritten and feed accumulator
                           // rows that are never stored)
@@ -174,6 +170,13 @@ __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Untiled bulk copy shared memory -> global memory (own or peer-mapped): 16-byte aligned addresses, size a multiple of 16.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // make generic-proxy shared-memory writes visible to the async proxy (TMA store reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -310,41 +313,6 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int tile, int& tm
     tm = m0 + (within - tn * rows);
 }
 
-// Split-K: out[m, n] = out_dtype( alpha * sum_s partial[s, m, n] + bias[n] ) for the BN columns of tile column tn, by
-// the 128 epilogue threads of the item that delivered the tile's last partial sums (t = 0..127).  Four columns per
-// thread and step (N % 8 == 0), partial sums read past the L1 (other SMs wrote them), added in split order.
-template <int BN>
-__device__ __forceinline__ void reduce_split_tile(const GemmArgs& g, int tn, float alpha, int t) {
-    const int n0 = tn * BN;
-    const int quads_per_row = min(BN, g.N - n0) >> 2;
-    const int total = g.M * quads_per_row;
-    const int64_t plane = (int64_t)g.M * g.N;
-    for (int i = t; i < total; i += 128) {
-        const int row = i / quads_per_row;
-        const int col = n0 + 4 * (i - row * quads_per_row);
-        const float* p = g.partial + (int64_t)row * g.N + col;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < g.splits; ++s) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(p + s * plane));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        float y[4] = {acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha};
-        if (g.bias) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] += bias_at(g.bias, g.bias_dtype, col + j);
-        }
-        const int64_t o = (int64_t)row * g.ld_out + col;
-        if (g.out_dtype == CK_B200_DTYPE_F32) {
-            *reinterpret_cast<float4*>((float*)g.out + o) = make_float4(y[0], y[1], y[2], y[3]);
-        } else {
-            uint2 w;
-            w.x = pack16(y[0], y[1], g.out_dtype);
-            w.y = pack16(y[2], y[3], g.out_dtype);
-            *reinterpret_cast<uint2*>((uint16_t*)g.out + o) = w;
-        }
-    }
-}
-
 // ---- kernel -----------------------------------------------------------------------------------------
 
 // FMT 0: NVFP4 (packed e2m1, e4m3 scales per 16 elements, 256 elements of K per stage).
@@ -366,10 +334,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint64_t* acc_full_bar = bars + 2 * C::kStages;             // [2] MMA -> epilogue
     uint64_t* acc_empty_bar = acc_full_bar + 2;                 // [2] epilogue -> MMA: accumulator drained
     uint64_t* overlap_bar = acc_empty_bar + 2;                  // [1] epilogue -> MMA: shared columns drained
-    uint64_t* epi_bar = overlap_bar + 1;                        // [2] split-K: the four epilogue warps meet / learn who is last
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_bar + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(overlap_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* tile_is_last = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -385,8 +351,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             mbar_init(smem_u32(&acc_empty_bar[s]), 128);
         }
         mbar_init(smem_u32(overlap_bar), 128);
-        mbar_init(smem_u32(&epi_bar[0]), 4);
-        mbar_init(smem_u32(&epi_bar[1]), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -550,7 +514,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // ---------------- epilogue (warps 2..5) ----------------
         const int quad = warp & 3;   // tensor-memory lanes [32*quad, 32*quad+32) are the ones this warp may read
         int acc = 0;
-        uint32_t acc_phase = 0, epi_phase = 0;
+        uint32_t acc_phase = 0;
         bool ok = true;
         long long wait_acc = 0;
         const long long t_begin = now();
@@ -643,33 +607,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             mbar_arrive(smem_u32(&acc_empty_bar[acc]));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
-            if (g.splits > 1) {
-                // Split-K: this item's partial sums are in the scratch.  The four epilogue warps meet, one thread
-                // counts the item in on the tile's counter, and the item that arrives last adds the partial sums of
-                // all of them up (in split order, so the result does not depend on who was last), applies alpha and
-                // bias and writes the output tile.  Both meetings are bounded waits like every other wait here.
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&epi_bar[0]));
-                ok = mbar_wait(smem_u32(&epi_bar[0]), epi_phase, abort_flag, WAIT_EPILOGUE_SYNC);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (warp == 2 && lane == 0) {
-                    const unsigned arrived = atomicAdd(&g.tile_counters[tile], 1u) + 1u;
-                    const bool last = arrived == (unsigned)g.splits;
-                    if (last) g.tile_counters[tile] = 0u;   // every item of the tile is in: zero again for the next launch
-                    *tile_is_last = last ? 1 : 0;
-                    mbar_arrive(smem_u32(&epi_bar[1]));
-                }
-                ok = mbar_wait(smem_u32(&epi_bar[1]), epi_phase, abort_flag, WAIT_EPILOGUE_SYNC);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                epi_phase ^= 1;
-                if (*tile_is_last) {
-                    __threadfence();
-                    reduce_split_tile<BN>(g, tn, alpha, (int)threadIdx.x - 64);
-                }
-            }
         }
         if (g.tma_store && lane == 0) tma_store_wait_all();   // global writes complete before the CTA exits
         if (DBG && blockIdx.x == 0 && threadIdx.x == 64)
@@ -703,7 +640,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 // KB = packed bytes of K per stage and row: 128 (256 elements, 128-byte swizzle, 5 stages of 38 KiB) or 64
 // (128 elements, 64-byte swizzle, 11 stages of 19 KiB).  The finer stages keep more bytes in flight for the same
 // shared memory (10 of 11 stages instead of 4 of 5 while one is being consumed), which hides more load latency.
-template <int KB>
+// GATHER (the kernel that also delivers its tiles to the other ranks): the epilogue assembles whole 512-byte tile rows
+// in shared memory, 32 rows per warp with a 16-byte pad per row (conflict-free 16-byte stores by 32 lanes), and one
+// stage of the ring pays for that.
+constexpr int kGatherRowPitch = 512 + 16;
+template <int KB, bool GATHER = false>
 struct PairCfg {
     static_assert(KB == 128 || KB == 64, "stage width");
     static constexpr int kChunks = KB / 32;                         // 64-element MMA steps per stage
@@ -712,7 +653,8 @@ struct PairCfg {
     static constexpr int kSfa = kChunks * SF_CHUNK_BYTES;
     static constexpr int kSfb = 2 * kChunks * SF_CHUNK_BYTES;       // both 128-row bands of the B tile
     static constexpr int kStageBytes = kA + kB + kSfa + kSfb;       // 38 KiB or 19 KiB
-    static constexpr int kStagingBytes = 4 * 4 * STAGING_BYTES_PER_WARP;   // four staging tiles per epilogue warp
+    static constexpr int kStagingBytes = GATHER ? 4 * 32 * kGatherRowPitch     // 32 full tile rows per epilogue warp
+                                                : 4 * 4 * STAGING_BYTES_PER_WARP;   // four staging tiles per epilogue warp
     static constexpr int kStages = (232448 - 1024 - 256 - kStagingBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
     static constexpr uint32_t kLayout = (KB == 128) ? LAYOUT_SWIZZLE_128B : LAYOUT_SWIZZLE_64B;
@@ -821,13 +763,15 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 
 // FMT as in gemm_nvfp4_kernel: 0 = NVFP4, 1 = MXFP8 (one scale chunk per stage and band instead of KB / 32).
 // QDT: -1 = operands come quantized; otherwise the dtype code of the activations that eight extra warps quantize.
-template <int KB, bool DBG, int FMT = 0, int QDT = -1>
+// GATHER: every finished tile also goes to the same place of the other ranks' output matrices (g.peer_out), as
+// 512-byte row segments copied out of shared memory by bulk async copies (no load of any kind from peer memory).
+template <int KB, bool DBG, int FMT = 0, int QDT = -1, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                        const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g, const FusedQuant fq) {
     constexpr bool QF = QDT >= 0;
-    using P = PairCfg<KB>;
+    using P = PairCfg<KB, GATHER>;
     constexpr int kStages2 = P::kStages, kStageBytes2 = P::kStageBytes, kA2 = P::kA, kB2 = P::kB, kSfa2 = P::kSfa;
     constexpr int kChunks = P::kChunks;
     extern __shared__ uint8_t smem_raw[];
@@ -1098,6 +1042,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const long long t_begin_ns = now_ns();
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
         uint8_t* my_staging = staging + quad * 4 * STAGING_BYTES_PER_WARP;   // four tiles per warp: step s uses tile s % 4
+        uint8_t* gather_rows = staging + quad * 32 * kGatherRowPitch;        // GATHER: this warp's 32 tile rows
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         const uint32_t overlap0 = map_to_cta(smem_u32(overlap_bar), 0);
         constexpr int kSteps = 256 / EPI_COLS;
@@ -1122,7 +1067,19 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 const int n0 = tn * 256 + s * EPI_COLS;
                 float y[32];
                 scale_row32(g, n0, v, alpha, y);
-                if (g.tma_store) {
+                if constexpr (GATHER) {
+                    // this lane's row of the tile: 64 bytes at column offset 32 s of its 512-byte row
+                    uint8_t* rowp = gather_rows + lane * kGatherRowPitch + s * (EPI_COLS * 2);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        uint4 o;
+                        o.x = pack16(y[8 * p + 0], y[8 * p + 1], g.out_dtype);
+                        o.y = pack16(y[8 * p + 2], y[8 * p + 3], g.out_dtype);
+                        o.z = pack16(y[8 * p + 4], y[8 * p + 5], g.out_dtype);
+                        o.w = pack16(y[8 * p + 6], y[8 * p + 7], g.out_dtype);
+                        *reinterpret_cast<uint4*>(rowp + (p << 4)) = o;
+                    }
+                } else if (g.tma_store) {
                     if (lane == 0) tma_store_wait_read<3>();   // the store issued four steps ago has read this tile
                     __syncwarp();
                     uint8_t* tile_smem = my_staging + (s & 3) * STAGING_BYTES_PER_WARP;
@@ -1143,29 +1100,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         tma_store_2d(&tmap_out, n0, row0, smem_u32(tile_smem));
                         tma_store_commit();
                     }
-                    if (g.n_peers > 0 && (i & 3) == 3) {
-                        // the same columns to the other ranks, four steps at a time: the warp's four staging tiles
-                        // now hold 128 adjacent columns of its 32 rows, which go out as 256-byte row segments,
-                        // sixteen lanes per row and two rows per store instruction
-                        const int c = lane & 15;
-                        const uint8_t* src_tile = my_staging + (c >> 2) * STAGING_BYTES_PER_WARP;
-                        const int col = tn * 256 + (s & ~3) * EPI_COLS + c * 8;
-#pragma unroll 4
-                        for (int j = 0; j < 16; ++j) {
-                            const int r = (lane >> 4) + 2 * j;
-                            const uint4 o =
-                                *reinterpret_cast<const uint4*>(src_tile + r * 64 + (((c & 3) ^ ((r >> 1) & 3)) << 4));
-                            if (row0 + r < g.M && col < g.N) {
-                                const int64_t off = ((int64_t)(row0 + r) * g.ld_out + col) * 2;
-#pragma unroll 1
-                                for (int p = 0; p < g.n_peers; ++p) st_global_v4(g.peer_out[p] + off, o);
-                            }
-                        }
-                    }
                 } else if (row < g.M && n0 < g.N) {
                     store_row32(g, row, n0, y);
                 }
             };
+            if constexpr (GATHER) bulk_wait_read_all();   // the previous tile's copies have read this lane's row
             {
                 // both steps of the columns shared by the two accumulators are fetched first and handed to the
                 // next tile's MMAs before any output work
@@ -1203,10 +1142,27 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     emit(i + 1, step_at(i + 1), vb);
                 }
             }
+            if constexpr (GATHER) {
+                // The lane's 512-byte row of the tile is complete in shared memory (written by this lane alone): one bulk
+                // copy takes it to this rank's matrix and one to the same place in every other rank's.  The copies run
+                // on the async proxy while the warp goes on to the next tile.
+                fence_proxy_async_smem();
+                const int col0 = tn * 256;
+                const int bytes = min(256, g.N - col0) * 2;
+                if (row < g.M && bytes > 0) {
+                    const uint32_t src = smem_u32(gather_rows + lane * kGatherRowPitch);
+                    const int64_t off = (row * g.ld_out + col0) * 2;
+                    bulk_store(reinterpret_cast<uint8_t*>(g.out) + off, src, (uint32_t)bytes);
+#pragma unroll 1
+                    for (int p = 0; p < g.n_peers; ++p) bulk_store(g.peer_out[p] + off, src, (uint32_t)bytes);
+                }
+                bulk_commit();
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
-        if (g.tma_store && lane == 0) tma_store_wait_all();
+        if constexpr (GATHER) bulk_wait_all();   // every copy has been performed before the CTA exits
+        else if (g.tma_store && lane == 0) tma_store_wait_all();
         if (DBG && pair == 0 && threadIdx.x == 64)
             printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank,
                    now() - t_begin, now_ns() - t_begin_ns, wait_acc);
@@ -1274,6 +1230,39 @@ __global__ void peer_barrier_kernel(const BarrierArgs b) {
     if (t == 0) *b.epoch = target;
 }
 
+// ---- split-K reduction ----------------------------------------------------------------------------
+
+// out[m,n] = out_dtype( alpha * sum_s partial[s,m,n] + bias[n] ), four columns per thread (N % 8 == 0).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                                            const float* tsa, const float* tsb, const float* alpha_ptr,
+                                                            const void* bias, int bias_dtype, void* out, int out_dtype) {
+    allow_dependent_launch();
+    const int64_t quads = (int64_t)M * N / 4;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= quads) return;
+    grid_dependency_wait();
+    const float alpha = alpha_ptr ? __ldg(alpha_ptr) : __fmul_rn(__ldg(tsa), __ldg(tsb));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(partial) + (int64_t)s * quads + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float y[4] = {acc.x * alpha, acc.y * alpha, acc.z * alpha, acc.w * alpha};
+    const int n = (int)((i * 4) % N);
+    if (bias) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[j] += bias_at(bias, bias_dtype, n + j);
+    }
+    if (out_dtype == CK_B200_DTYPE_F32) {
+        reinterpret_cast<float4*>(out)[i] = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+        uint2 o;
+        o.x = pack16(y[0], y[1], out_dtype);
+        o.y = pack16(y[2], y[3], out_dtype);
+        reinterpret_cast<uint2*>(out)[i] = o;
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1310,36 +1299,40 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_
     return CK_B200_OK;
 }
 
-// make_operand_map for an operand that stays where it is over many calls (a resident weight): the encoded map is kept
-// in a small per-process table keyed by address, shape and box, so the driver call happens once per weight.  A map
+// Tensor maps of operands that stay where they are over many calls (a resident weight and its scales) are kept in a
+// small per-process table keyed by kind, address, shape and box, so the driver call happens once per weight.  A map
 // only describes memory (base, extents, strides), so a stale entry for a freed and reused address is still a valid
 // description of whatever matrix of that shape now lives there.
-int cached_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_bytes, int box_rows, int box_bytes = BK_BYTES) {
+template <typename Build>
+int cached_map(CUtensorMap* map, int kind, const void* ptr, int64_t d0, int64_t d1, int b0, int b1, Build build) {
     struct Entry {
         const void* ptr;
-        int64_t rows, k_bytes;
-        int box_rows, box_bytes, dev;
+        int64_t d0, d1;
+        int b0, b1, dev, kind;
         CUtensorMap map;
     };
-    constexpr int kEntries = 256;
+    constexpr int kEntries = 512;
     static std::mutex mu;
     static Entry table[kEntries] = {};
     int dev = 0;
     CKB_CUDA_OK(cudaGetDevice(&dev));
-    const size_t h = ((reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull >> 40) % kEntries;
+    const size_t h = ((((uint64_t)reinterpret_cast<uintptr_t>(ptr) >> 8) + (uint64_t)kind) * 0x9E3779B97F4A7C15ull >> 40) % kEntries;
     {
         std::lock_guard<std::mutex> lock(mu);
         const Entry& e = table[h];
-        if (e.ptr == ptr && e.rows == rows && e.k_bytes == k_bytes && e.box_rows == box_rows && e.box_bytes == box_bytes &&
-            e.dev == dev) {
+        if (e.ptr == ptr && e.d0 == d0 && e.d1 == d1 && e.b0 == b0 && e.b1 == b1 && e.dev == dev && e.kind == kind) {
             *map = e.map;
             return CK_B200_OK;
         }
     }
-    if (int rc = make_operand_map(map, ptr, rows, k_bytes, box_rows, box_bytes)) return rc;
+    if (int rc = build()) return rc;
     std::lock_guard<std::mutex> lock(mu);
-    table[h] = Entry{ptr, rows, k_bytes, box_rows, box_bytes, dev, *map};
+    table[h] = Entry{ptr, d0, d1, b0, b1, dev, kind, *map};
     return CK_B200_OK;
+}
+int cached_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k_bytes, int box_rows, int box_bytes = BK_BYTES) {
+    return cached_map(map, 1, ptr, rows, k_bytes, box_rows, box_bytes,
+                      [&] { return make_operand_map(map, ptr, rows, k_bytes, box_rows, box_bytes); });
 }
 
 // 16-bit output [M, N] row-major, boxes of 32 columns (64 bytes) x 32 rows, 64-byte swizzle.
@@ -1373,10 +1366,14 @@ int make_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks, int box_ch
     return CK_B200_OK;
 }
 
+int cached_scale_map(CUtensorMap* map, const void* ptr, int64_t chunks, int box_chunks) {
+    return cached_map(map, 2, ptr, chunks, 0, box_chunks, 0, [&] { return make_scale_map(map, ptr, chunks, box_chunks); });
+}
+
 // Pairs of CTAs that can be resident at once (clusters of 2 need two free SMs of one GPC), cached per device.
-template <int KB, int QDT = -1>
+template <int KB, int QDT = -1, bool GATHER = false>
 int max_active_pairs(int* out) {
-    constexpr int kSmemBytes2 = PairCfg<KB>::kSmemBytes;
+    constexpr int kSmemBytes2 = PairCfg<KB, GATHER>::kSmemBytes;
     constexpr int kThreads = QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS;
     static std::mutex mu;
     static int cache[64] = {0};
@@ -1385,7 +1382,7 @@ int max_active_pairs(int* out) {
     if (int rc = check_device(&sms)) return rc;   // also bounds the device ordinal
     std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == 0) {
-        auto kernel = gemm_nvfp4_pair_kernel<KB, false, 0, QDT>;
+        auto kernel = gemm_nvfp4_pair_kernel<KB, false, 0, QDT, GATHER>;
         CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * (unsigned)sms);
@@ -1408,32 +1405,34 @@ int max_active_pairs(int* out) {
 }
 
 // QDT >= 0: the kernel also quantizes the activations described by *fused (dtype code QDT) into `a` and g.sfa.
-template <int KB, int FMT = 0, int QDT = -1>
+template <int KB, int FMT = 0, int QDT = -1, bool GATHER = false>
 int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream,
                      const FusedQuant* fused = nullptr) {
-    using P = PairCfg<KB>;
+    using P = PairCfg<KB, GATHER>;
     constexpr int kSmemBytes2 = P::kSmemBytes;
     constexpr int kSfChunks = FMT == 1 ? 1 : P::kChunks;
     constexpr int kThreads = QDT >= 0 ? NUM_THREADS + kQuantWarps * 32 : NUM_THREADS;
     const int64_t row_bytes = FMT == 1 ? K : K / 2;
-    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true, FMT, QDT> : gemm_nvfp4_pair_kernel<KB, false, FMT, QDT>;
+    auto kernel = g.debug ? gemm_nvfp4_pair_kernel<KB, true, FMT, QDT, GATHER> : gemm_nvfp4_pair_kernel<KB, false, FMT, QDT, GATHER>;
     int pairs = 0;
-    if (int rc = max_active_pairs<KB, QDT>(&pairs)) return rc;
+    if (int rc = max_active_pairs<KB, QDT, GATHER>(&pairs)) return rc;
     FusedQuant fq{};
     if (QDT >= 0) {
         if (!fused) return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused quantizer: missing description");
         fq = *fused;
     }
-    cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
-    if (attr_err != cudaSuccess)
-        return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
-                    cudaGetErrorString(attr_err));
+    if (g.debug) {   // the regular build was opted in to its shared memory by max_active_pairs, once per device
+        cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+        if (attr_err != cudaSuccess)
+            return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
+                        cudaGetErrorString(attr_err));
+    }
     CUtensorMap ma, mb, msa, msb, mo;
     if (int rc = make_operand_map(&ma, a, g.M, row_bytes, BM, KB)) return rc;
-    if (int rc = make_operand_map(&mb, b, g.N, row_bytes, 128, KB)) return rc;
+    if (int rc = cached_operand_map(&mb, b, g.N, row_bytes, 128, KB)) return rc;   // the resident weight and its scales
     if (int rc = make_scale_map(&msa, g.sfa, ceil_div64(g.M, 128) * g.sf_cbg, kSfChunks)) return rc;
-    if (int rc = make_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, kSfChunks)) return rc;
-    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32) ? 1 : 0;
+    if (int rc = cached_scale_map(&msb, g.sfb, ceil_div64(g.N, 128) * g.sf_cbg, kSfChunks)) return rc;
+    g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32 && !GATHER) ? 1 : 0;   // GATHER copies rows out itself
     if (g.tma_store) {
         if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
     } else {
@@ -1445,8 +1444,12 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     int64_t group = (8ll << 20) / (row_block_bytes > 0 ? row_block_bytes : 1);
     if (group < 4) group = 4;
     g.raster_group = (int)(group < g.m_tiles ? group : g.m_tiles);
-    // with the quantizer inside, tiles go row block by row block: the first wave then waits for a few bands only
-    if (QDT >= 0) g.raster_group = 1;
+    // with the quantizer inside, tiles go row block by row block: the first wave then waits for a few bands only.
+    // Delivering tiles to the other ranks: row block by row block too, so that at any time the stores of all CTAs fall
+    // into a few megabytes of each peer's matrix.  Peer-mapped memory is translated in 2 MiB pages and the translation
+    // cache covers a few GiB: walking all rows once per tile column touched every page again and again, and once the
+    // matrices mapped from the peers exceeded that reach the stores fell from ~500 to below 100 GB/s.
+    if (QDT >= 0 || GATHER) g.raster_group = 1;
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
@@ -1469,9 +1472,8 @@ int choose_splits(int n_tiles, int k_iters, int sms, int64_t M, int64_t N, size_
     return s < 1 ? 1 : s;
 }
 
-// Scratch of a split-K launch: `counters` (kSplitHeaderBytes, zero between launches) and room for the partial sums.
+// Scratch of a split-K launch: room for the fp32 partial sums.
 struct SplitScratch {
-    unsigned* counters = nullptr;
     float* partial = nullptr;
     size_t partial_bytes = 0;
 };
@@ -1511,19 +1513,15 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
-    g.tile_counters = nullptr;
-    if (g.m_tiles == 1 && scratch.partial != nullptr && scratch.counters != nullptr && g.n_tiles <= kSplitMaxTiles) {
+    if (g.m_tiles == 1 && scratch.partial != nullptr) {
         g.splits = choose_splits(g.n_tiles, g.k_iters, sms, g.M, g.N, scratch.partial_bytes);
         if (g.splits > 1) {
             g.k_per_split = (int)ceil_div64(g.k_iters, g.splits);
             g.splits = (int)ceil_div64(g.k_iters, g.k_per_split);   // no empty work items
         }
-        if (g.splits > 1) {
-            g.partial = scratch.partial;
-            g.tile_counters = scratch.counters;
-        }
+        if (g.splits > 1) g.partial = scratch.partial;
     }
-    // split-K items write fp32 partial sums and the last item of a tile stores the output itself: no output map
+    // split-K items write fp32 partial sums and the reduction kernel stores the output: no output map
     g.tma_store = (g.out_dtype != CK_B200_DTYPE_F32 && g.splits == 1) ? 1 : 0;
     if (g.tma_store) {
         if (int rc = make_output_map(&mo, g.out, g.M, g.N, g.ld_out)) return rc;
@@ -1536,6 +1534,14 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
+    if (g.splits > 1) {
+        const int64_t quads = (int64_t)g.M * g.N / 4;
+        const cudaError_t err2 = launch_dependent(kLaunchFamilyGemm, splitk_reduce_kernel, dim3((unsigned)ceil_div64(quads, 256)), dim3(256), 0,
+                                                  stream, g.partial, g.splits, g.M, g.N, g.tsa, g.tsb, g.alpha, g.bias,
+                                                  g.bias_dtype, g.out, g.out_dtype);
+        g_launches.fetch_add(1);
+        CKB_CUDA_OK(err2);
+    }
     return CK_B200_OK;
 }
 
@@ -1597,7 +1603,6 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
-    g.tile_counters = nullptr;
     g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
@@ -1610,7 +1615,7 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
     if (variant == 0) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
-    if (((uintptr_t)scratch.partial & 15) || ((uintptr_t)scratch.counters & 15))
+    if ((uintptr_t)scratch.partial & 15)
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
     if (gather) {
         if (out_dtype == CK_B200_DTYPE_F32 || M <= 128 || N <= 128)
@@ -1619,7 +1624,7 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
         g.ld_out = gather->ld;
         g.n_peers = gather->n_peers;
         for (int p = 0; p < gather->n_peers; ++p) g.peer_out[p] = gather->peers[p];
-        return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
+        return launch_gemm_pair<128, 0, -1, true>(a_dev, b_dev, g, K, s);
     }
     if (fused) {
         if (M <= 128 || N <= 128)
@@ -1637,13 +1642,11 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch);
 }
 
-// A caller's workspace as split-K scratch: the tile counters in its first kSplitHeaderBytes, partial sums behind them.
 SplitScratch scratch_from_workspace(void* workspace_dev, size_t workspace_bytes) {
     SplitScratch sc;
-    if (workspace_dev && workspace_bytes > kSplitHeaderBytes + (1u << 16)) {
-        sc.counters = (unsigned*)workspace_dev;
-        sc.partial = (float*)((char*)workspace_dev + kSplitHeaderBytes);
-        sc.partial_bytes = workspace_bytes - kSplitHeaderBytes;
+    if (workspace_dev && workspace_bytes > 0) {
+        sc.partial = (float*)workspace_dev;
+        sc.partial_bytes = workspace_bytes;
     }
     return sc;
 }
@@ -1659,24 +1662,6 @@ extern "C" int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, c
                           scratch_from_workspace(workspace_dev, workspace_bytes), stream);
 }
 
-namespace ckb {
-// scaled_mm_nvfp4 with the split-K scratch given as its two parts (the whole-linear entry point keeps the counters at
-// a fixed place of its workspace and the partial sums behind the quantized activation).
-int scaled_mm_nvfp4_split(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
-                          const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const void* bias_dev_or_null,
-                          int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N, int64_t K, void* counters_dev,
-                          void* partial_dev, size_t partial_bytes, void* stream) {
-    SplitScratch sc;
-    if (counters_dev && partial_dev && partial_bytes >= (1u << 16)) {
-        sc.counters = (unsigned*)counters_dev;
-        sc.partial = (float*)partial_dev;
-        sc.partial_bytes = partial_bytes;
-    }
-    return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, nullptr, bias_dev_or_null,
-                          bias_dtype, out_dev, out_dtype, M, N, K, sc, stream);
-}
-size_t split_header_bytes() { return kSplitHeaderBytes; }
-}  // namespace ckb
 
 
 // ---- GEMM that quantizes its own activations -------------------------------------------------------------
@@ -1836,7 +1821,6 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
-    g.tile_counters = nullptr;
     g.a_box_bytes = BM * BK_BYTES;
     g.raster_group = 1;
     g.tma_store = 0;
@@ -1857,11 +1841,9 @@ extern "C" int ck_b200_scaled_mm_mxfp8(const void* a_dev, const void* sfa_dev, c
 // ---- entry point with built-in scratch --------------------------------------------------------------
 
 namespace {
-constexpr size_t kStaticPartialBytes = 8u << 20;
-constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kSplitHeaderBytes;
-// Split-K scratch for callers that cannot hand over device memory of their own: the tile counters (4 KiB, zero when
-// the library is loaded and left zero by every launch) followed by 8 MiB for partial sums.  Lives in the library
-// image: every device that loads the library holds it until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+// Split-K partial sums for callers that cannot hand over device memory of their own.  Lives in the library image:
+// every device that loads the library holds these 8 MiB until the process exits.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // Device address of g_static_scratch on the current device, looked up once per device.  In host code the array's
@@ -1894,11 +1876,11 @@ extern "C" int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const v
         return fail(CK_B200_ERR_INVALID_ARGUMENT,
                     "scaled_mm_nvfp4_static_scratch: M = %lld is beyond the limit of 128 rows (larger problems need no "
                     "scratch: use ck_b200_scaled_mm_nvfp4)", (long long)M);
-    if (M > 0 && N > 0 && (size_t)M * (size_t)N * 4 * 2 > kStaticPartialBytes)
+    if (M > 0 && N > 0 && (size_t)M * (size_t)N * 4 * 2 > kStaticScratchBytes)
         return fail(CK_B200_ERR_INVALID_ARGUMENT,
                     "scaled_mm_nvfp4_static_scratch: M * N = %lld is beyond the limit of %lld outputs (two fp32 partial "
                     "sums per output must fit the %lld-byte built-in scratch)",
-                    (long long)(M * N), (long long)(kStaticPartialBytes / 8), (long long)kStaticPartialBytes);
+                    (long long)(M * N), (long long)(kStaticScratchBytes / 8), (long long)kStaticScratchBytes);
     unsigned char* scratch = nullptr;
     if (int rc = static_scratch_address(&scratch)) return rc;
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,

@@ -36,7 +36,6 @@ def _workspace(device: torch.device) -> torch.Tensor | None:
         if torch.cuda.is_current_stream_capturing():
             return None
         ws = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
-        ws[:4096].zero_()      # the split-K tile counters (CK_B200_WORKSPACE_HEADER_BYTES) start from zero
         _WORKSPACES[key] = ws
     return ws
 

@@ -71,14 +71,10 @@ int ck_b200_dequantize_nvfp4(const void* q_dev, const float* per_tensor_scale_de
  *   bias_dev_or_null [N] of dtype code bias_dtype (1 or 2; 0 also accepted)
  *   out_dev [M, N] row-major of dtype code out_dtype (1 or 2; 0 also accepted)
  *   K % 32 == 0 and N % 8 == 0 (the reference's constraints, comfy_kitchen/backends/cuda/__init__.py:1779,3621-3625)
- *   workspace_dev / workspace_bytes: scratch for split-K (problems with M <= 128 are cut along K over all SMs and
- *   the work item that finishes a tile last adds the partial sums up, inside the same kernel); may be NULL / 0, in
- *   which case such shapes run unsplit.  ck_b200_query(CK_B200_QUERY_WORKSPACE_BYTES) gives a size that is always
- *   enough.  The first CK_B200_WORKSPACE_HEADER_BYTES of the workspace hold per-tile counters: they must be zero
- *   when the workspace is first used (zero it once after allocating) and every call leaves them zero.  Calls that
- *   share a workspace must not overlap on the GPU.
+ *   workspace_dev / workspace_bytes: scratch for split-K reductions; may be NULL / 0, in which case
+ *   shapes that would use split-K run unsplit.  ck_b200_query(CK_B200_QUERY_WORKSPACE_BYTES) gives a
+ *   size that is always enough.  Calls that share a workspace must not overlap on the GPU.
  */
-#define CK_B200_WORKSPACE_HEADER_BYTES 4096
 int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* b_dev, const void* sfb_dev,
                             const float* tensor_scale_a_dev, const float* tensor_scale_b_dev,
                             const float* alpha_dev_or_null, const void* bias_dev_or_null, int bias_dtype,
@@ -92,15 +88,14 @@ int ck_b200_scaled_mm_nvfp4(const void* a_dev, const void* sfa_dev, const void* 
  * running inside another framework's captured or pre-planned execution, a real-time loop with a frozen memory plan,
  * a host that keeps the CUDA allocator to itself.  Such callers have no workspace to pass to
  * ck_b200_scaled_mm_nvfp4, and without one a problem with M <= 128 runs unsplit on a fraction of the SMs.
- * Here the fp32 partial sums and the per-tile counters go to an 8 MiB (+ 4 KiB) array that is part of the library image (every GPU that loads the
+ * Here the fp32 partial sums go to an 8 MiB array that is part of the library image (every GPU that loads the
  * library holds it until the process exits); the call itself performs no allocation of any kind.
  *
  * Same arguments and result as ck_b200_scaled_mm_nvfp4 minus the workspace.  Limits, rejected with
  * CK_B200_ERR_INVALID_ARGUMENT and a message: M <= 128, and M * N <= 1 048 576 outputs (two partial sums each).
  * The first call on each device looks the array's device address up (with that device current): make that call
  * before starting a stream capture.  All calls share the one array and it is not cleared between calls (every word
- * of partial sums that is read has been written by the same call first; the counters start at zero when the library is
- * loaded and every call leaves them zero): two such calls that overlap on the GPU - different streams,
+ * that is read has been written by the same call first): two such calls that overlap on the GPU - different streams,
  * or graph branches - race on it; calls on one stream are ordered and safe.
  */
 int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const void* sfa_dev, const void* b_dev,
@@ -169,8 +164,8 @@ int ck_b200_peer_free(void* ptr);
  * quantize x into the workspace while the tensor-core main loop runs, and each tile's loads wait (bounded) for the
  * 128-row band of x they read.  Results are bit-identical to the separate operators.  The progress
  * words live in bytes [256, 256 + 32 KiB) of the workspace, which only that kernel writes, and the counters of the
- * dynamic quantizer (input_scale_dev_or_null == NULL) in bytes [64, 80) and those of the split-K GEMM behind the
- * progress words: zero the first 64 KiB once when the workspace is allocated (they then stay consistent over any sequence of calls, shapes and graph replays).  Calls
+ * dynamic quantizer (input_scale_dev_or_null == NULL) in bytes [64, 80): zero the first 33 KiB once when the
+ * workspace is allocated (they then stay consistent over any sequence of calls, shapes and graph replays).  Calls
  * that share a workspace must not overlap on the GPU.
  */
 int64_t ck_b200_linear_nvfp4_workspace_bytes(int64_t M, int64_t K);

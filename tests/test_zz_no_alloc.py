@@ -61,9 +61,9 @@ def test_static_scratch_entry_point_matches_regular_one():
             qx.data_ptr(), sfx.data_ptr(), qw.data_ptr(), sfw.data_ptr(), tsx.data_ptr(), tsw.data_ptr(), None,
             bias.data_ptr(), 2, out.data_ptr(), code, M, N, K, stream)
         assert rc == 0, _lib.last_error()
-        # the split-K path ran (partial sums through the built-in scratch, summed inside the same kernel), cut into
-        # as many pieces as the regular call's
-        assert ckb.launches() - n0 == regular_launches == 1
+        # the split-K path ran (partial sums through the built-in scratch, then the reduction kernel), cut into as
+        # many pieces as the regular call's
+        assert ckb.launches() - n0 == regular_launches == 2
         assert L.ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS) == regular_splits > 1
         torch.cuda.synchronize()
         assert torch.isfinite(out.float()).all()
