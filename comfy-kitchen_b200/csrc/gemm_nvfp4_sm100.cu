@@ -1041,7 +1041,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const long long t_begin = now();
         const long long t_begin_ns = now_ns();
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
-        uint8_t* my_staging = staging + quad * 4 * STAGING_BYTES_PER_WARP;   // four tiles per warp: step s uses tile s % 4
+        uint8_t* my_staging = staging + quad * 4 * STAGING_BYTES_PER_WARP;   // four tiles per warp: the i-th emitted step uses tile i % 4
         uint8_t* gather_rows = staging + quad * 32 * kGatherRowPitch;        // GATHER: this warp's 32 tile rows
         const uint32_t acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         const uint32_t overlap0 = map_to_cta(smem_u32(overlap_bar), 0);
@@ -1080,9 +1080,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         *reinterpret_cast<uint4*>(rowp + (p << 4)) = o;
                     }
                 } else if (g.tma_store) {
-                    if (lane == 0) tma_store_wait_read<3>();   // the store issued four steps ago has read this tile
+                    // Four staging tiles per warp, taken in the order in which the steps are emitted (i, not the column
+                    // step s: accumulator 0 walks the steps as 6,7,4,5,0,1,2,3, and indexing by s would hand a tile out
+                    // again two steps later, while the TMA store that reads it may still be in flight - its last rows
+                    // then carry the later step's values).  With i the store that last used the tile is always the one
+                    // issued four steps ago, which wait_group.read 3 has retired.
+                    if (lane == 0) tma_store_wait_read<3>();
                     __syncwarp();
-                    uint8_t* tile_smem = my_staging + (s & 3) * STAGING_BYTES_PER_WARP;
+                    uint8_t* tile_smem = my_staging + (i & 3) * STAGING_BYTES_PER_WARP;
                     uint8_t* rowp = tile_smem + lane * 64;
                     const int sw = (lane >> 1) & 3;
 #pragma unroll

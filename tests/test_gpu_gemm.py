@@ -196,6 +196,31 @@ def test_split_k_repeats_and_graph_replays(mnk, ckb):
     assert ckb.read_device_status() == 0
 
 
+EXACT = [(4608, 9216, 3072), (4608, 4608, 3072), (4608, 6144, 3072), (4608, 3072, 12288), (4608, 1536, 3072),
+         (32760, 5120, 5120)]
+
+
+@pytest.mark.parametrize("mnk", EXACT, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_tile_variants_are_bit_identical(mnk, ckb):
+    """Every tile variant adds the K dimension up in the same order with the same instruction, so at full size the
+    CTA-pair kernel must reproduce the one-CTA kernel bit for bit, launch after launch - a relative-RMS tolerance
+    would not notice a few hundred elements of a 40-million-element matrix going wrong (for instance a staging tile
+    handed out again while the store that reads it is still in flight).  Widths of N-sharded weights included."""
+    M, N, K = mnk
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=K + N, outliers=True)
+    prev = ckb.set_tuning(1, 1)                      # 128 x 128 tiles, one CTA each
+    try:
+        ref = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+        for v in (2, 3, 3, 3, 4):                    # the default (CTA pairs) several times: the hazard is one of timing
+            ckb.set_tuning(1, v)
+            y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw)
+            bad = int((y != ref).sum())
+            assert bad == 0, f"variant {v}: {bad} elements differ from the 128x128 one-CTA kernel"
+    finally:
+        ckb.set_tuning(1, prev)
+    assert ckb.read_device_status() == 0
+
+
 def test_gemm_rejects_bad_arguments(ckb):
     qx = torch.zeros((128, 64), dtype=torch.uint8, device="cuda")
     qw = torch.zeros((64, 64), dtype=torch.uint8, device="cuda")
