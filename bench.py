@@ -266,6 +266,7 @@ class Bench:
             dist.init_process_group("nccl", device_id=self.dev)
         self.side = torch.cuda.Stream()       # capture stream
         self.side2 = torch.cuda.Stream()      # second branch of a captured step (the quantizers)
+        self.side3 = torch.cuda.Stream()      # third branch (several GPUs: every other GEMM)
         self.graphs = []
         self.use_graph = not args.no_graph
 
@@ -386,6 +387,7 @@ class StepPlan:
             self.declined = (f"{peer_bytes / 2**30:.1f} GiB of peer-mapped output matrices per rank: NCCL all-gather "
                              "instead")
         self.use_graph = B.use_graph and (not B.distributed or self.fused)
+        self.half_pairs = max(1, int(ckb._lib.load().ck_b200_query(ckb._lib.QUERY_SM_COUNT)) // 4)   # half of the CTA pairs
         self.peers = None
         if self.fused:
             self.peers = ckb.PeerGroup(B.dev)
@@ -440,12 +442,14 @@ class StepPlan:
                     l.input_scale = s
 
     def step_overlapped(self):
-        """The same work as two branches (captured into one CUDA graph): the quantizers run on a second stream, so
-        the quantizer of linear i+1 overlaps the GEMM (and, on several GPUs, the peer stores) of linear i.  Legitimate
-        because the four linears of the step are independent work items; inside a real block, where each linear's
-        input depends on the previous output, only the serial step applies."""
-        torch = self.B.torch
-        cur, qs = torch.cuda.current_stream(), self.B.side2
+        """The same work as several branches of one CUDA graph.  The quantizers run on a second stream, so the quantizer
+        of linear i+1 overlaps the GEMM of linear i.  On several GPUs the GEMMs themselves alternate between two
+        streams, each kernel on half of the CTA pairs (CK_B200_TUNE_GEMM_MAX_PAIRS): those kernels are bound by the
+        link, not by the tensor cores, and side by side one kernel's stores fill the link while the other ramps up
+        or drains.  Legitimate because the four linears of the step are independent work items; inside a real block,
+        where each linear's input depends on the previous output, only the serial step applies."""
+        torch, ckb = self.B.torch, self.ckb
+        cur, qs, g1 = torch.cuda.current_stream(), self.B.side2, self.B.side3
         qs.wait_stream(cur)
         quant, events = [], []
         with torch.cuda.stream(qs):
@@ -456,11 +460,23 @@ class StepPlan:
                 events.append(e)
         if self.fused:
             self.peers.barrier()
+        two = self.fused and self.B.args.gemm_streams == 2
+        if two:
+            g1.wait_stream(cur)                 # after the opening barrier
+            prev_cap = ckb.set_tuning(9, self.half_pairs)
         outs = []
-        for (qx, sfx, t), lin, e in zip(quant, self.layers, events):
-            cur.wait_event(e)
-            outs.append(lin.fused_from_quantized(qx, sfx, t, self.M) if self.fused
-                        else lin.local_from_quantized(qx, sfx, t, self.M))
+        try:
+            for i, ((qx, sfx, t), lin, e) in enumerate(zip(quant, self.layers, events)):
+                stream = g1 if (two and i % 2 == 1) else cur
+                stream.wait_event(e)
+                with torch.cuda.stream(stream):
+                    outs.append(lin.fused_from_quantized(qx, sfx, t, self.M) if self.fused
+                                else lin.local_from_quantized(qx, sfx, t, self.M))
+        finally:
+            if two:
+                ckb.set_tuning(9, prev_cap)
+        if two:
+            cur.wait_stream(g1)
         cur.wait_stream(qs)
         if self.fused:
             self.peers.barrier()
@@ -688,35 +704,51 @@ def quantize_sweep(B: Bench):
 
 
 def small_m_sweep(B: Bench):
-    """T5-XXL-style feed-forward shapes (d = 4096, ff = 10240): latency of one linear (quantize + GEMM, split-K below
-    129 rows) per M."""
+    """T5-XXL-style feed-forward shapes (d = 4096, ff = 10240): one linear (quantize + GEMM, split-K below 129 rows)
+    per M.  Two figures per shape.  `*_chain_us`: eight layers with eight different weights (189 MB, more than the L2,
+    so every weight streams from HBM) launched one after the other inside one CUDA graph, time per layer - the way a
+    stack of such layers runs.  `*_single_us`: a graph holding ONE launch, replayed back to back: this adds the gap
+    between two graph launches (about 3 us for an empty kernel) and is the latency of an isolated call."""
     import comfy_kitchen_b200 as ckb
     torch = B.torch
     small_m = []
     gsm = torch.Generator(device=B.dev).manual_seed(5)
+    LAYERS = 8
     for (sk, sn) in [(4096, 10240), (10240, 4096)]:
-        ww = torch.randn((sn, sk), generator=gsm, device=B.dev, dtype=torch.bfloat16) * 0.02
-        wts = ckb.dynamic_scale_nvfp4(ww)
-        wq, wsf = ckb.quantize_nvfp4(ww, wts)
+        weights = []
+        for _ in range(LAYERS):
+            ww = torch.randn((sn, sk), generator=gsm, device=B.dev, dtype=torch.bfloat16) * 0.02
+            wts = ckb.dynamic_scale_nvfp4(ww)
+            wq, wsf = ckb.quantize_nvfp4(ww, wts)
+            weights.append((wq, wsf, wts))
+            del ww
         for sm in (1, 16, 64, 512):
             xx = torch.randn((sm, sk), generator=gsm, device=B.dev, dtype=torch.bfloat16)
             tt = ckb.dynamic_scale_nvfp4(xx)
             qq, ss = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
 
-            def lin_call(xx=xx, tt=tt, wq=wq, wts=wts, wsf=wsf):
+            def linear(w, xx=xx, tt=tt):
                 q1, s1 = ckb.quantize_nvfp4(xx, tt, pad_16x=True)
-                return ckb.scaled_mm_nvfp4(q1, wq, tt, wts, s1, wsf)
-            r_l, _ = B.graphed(lin_call)
-            r_g, n_g = B.graphed(lambda: ckb.scaled_mm_nvfp4(qq, wq, tt, wts, ss, wsf))
-            reps = 50
-            t_l = B.timed(r_l, reps, all_ranks=False) / reps
-            t_g = B.timed(r_g, reps, all_ranks=False) / reps
-            small_m.append({"M": sm, "K": sk, "N": sn, "linear_us": t_l * 1e3, "gemm_us": t_g * 1e3,
-                            "gemm_kernels": n_g, "gemm_tflops": 2.0 * sm * sn * sk / (t_g * 1e-3) / 1e12,
-                            "weight_gbs": sn * sk * 0.5625 / (t_g * 1e-3) / 1e9})
-            del r_l, r_g
+                return ckb.scaled_mm_nvfp4(q1, w[0], tt, w[2], s1, w[1])
+
+            def gemm(w, qq=qq, ss=ss, tt=tt):
+                return ckb.scaled_mm_nvfp4(qq, w[0], tt, w[2], ss, w[1])
+
+            r_lc, _ = B.graphed(lambda: [linear(w) for w in weights])
+            r_gc, n_gc = B.graphed(lambda: [gemm(w) for w in weights])
+            r_l1, _ = B.graphed(lambda: linear(weights[0]))
+            r_g1, _ = B.graphed(lambda: gemm(weights[0]))
+            reps = 20
+            t_lc = B.timed(r_lc, reps, all_ranks=False) / (reps * LAYERS)
+            t_gc = B.timed(r_gc, reps, all_ranks=False) / (reps * LAYERS)
+            t_l1 = B.timed(r_l1, 50, all_ranks=False) / 50
+            t_g1 = B.timed(r_g1, 50, all_ranks=False) / 50
+            small_m.append({"M": sm, "K": sk, "N": sn, "linear_chain_us": t_lc * 1e3, "gemm_chain_us": t_gc * 1e3,
+                            "linear_single_us": t_l1 * 1e3, "gemm_single_us": t_g1 * 1e3,
+                            "gemm_kernels": n_gc // LAYERS, "gemm_tflops": 2.0 * sm * sn * sk / (t_gc * 1e-3) / 1e12,
+                            "weight_gbs": sn * sk * 0.5625 / (t_gc * 1e-3) / 1e9})
             B.graphs.clear()
-        del ww, wq, wsf
+        del weights
     torch.cuda.empty_cache()
     return small_m
 
@@ -1145,6 +1177,7 @@ def run_ours(args, wl):
             "warmup": warm, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": workload_config(wl),
             "run": {"parallelism": plan.mode_text(),
+                    "gemm_streams": (args.gemm_streams if (fused and overlap) else 1),
                     "launch": "one CUDA graph per step" if plan.use_graph else "eager launches",
                     "linear": ("one kernel per linear: the GEMM kernel quantizes the activations beside its main loop "
                                "(ck_b200_linear_nvfp4)") if one_call and not distributed else
@@ -1178,6 +1211,9 @@ def main():
                     help="skip the single-GPU extras: sustained run, FP4 ceiling, quantizer sweep and comparators, "
                          "small-M sweep, MXFP8")
     ap.add_argument("--no-wan", action="store_true", help="skip the short record of the Wan-class workload")
+    ap.add_argument("--gemm-streams", type=int, default=2, choices=[1, 2],
+                    help="N > 1: run the link-bound GEMM + all-gather kernels on one stream, or alternate them between two "
+                         "streams with half of the CTA pairs each")
     ap.add_argument("--serial", action="store_true",
                     help="time the eight kernels of a step as one chain instead of overlapping each quantizer with the "
                          "previous linear's GEMM")

@@ -12,6 +12,7 @@ std::atomic<int> g_dependent_launch{1};
 std::atomic<int> g_gemm_variant{0};
 std::atomic<int> g_gemm_debug{0};
 std::atomic<int> g_last_splits{1};
+std::atomic<int> g_gemm_max_pairs{0};
 std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
@@ -103,6 +104,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_QUANT_SYNC_TEST: return ckb::g_quant_sync_test.exchange(value);
         case CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB: return ckb::g_dynamic_fused_max_mb.exchange(value);
         case CK_B200_TUNE_DYNAMIC_SMEM: return ckb::g_dynamic_smem.exchange(value);
+        case CK_B200_TUNE_GEMM_MAX_PAIRS: return ckb::g_gemm_max_pairs.exchange(value);
         default: return -1;
     }
 }

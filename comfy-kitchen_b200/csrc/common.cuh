@@ -24,6 +24,7 @@ extern std::atomic<int> g_quant_variant;
 extern std::atomic<int> g_gemm_variant;
 extern std::atomic<int> g_gemm_debug;
 extern std::atomic<int> g_dependent_launch;
+extern std::atomic<int> g_gemm_max_pairs;   // > 0: the CTA-pair GEMM launches at most this many pairs (CK_B200_TUNE_GEMM_MAX_PAIRS)
 extern std::atomic<int> g_last_splits;   // K-splits of the most recent GEMM launch (CK_B200_QUERY_LAST_GEMM_SPLITS)
 
 // Checks that the current device is compute capability 10.x (cached per device ordinal).

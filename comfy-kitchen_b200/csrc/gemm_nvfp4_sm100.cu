@@ -1460,6 +1460,9 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
     g.partial = nullptr;
     g_last_splits.store(1);
     const int64_t tiles = (int64_t)g.m_tiles * g.n_tiles;
+    // a caller that runs two of these kernels side by side (two streams) gives each a share of the CTA pairs
+    const int cap = g_gemm_max_pairs.load();
+    if (cap > 0 && cap < pairs) pairs = cap;
     const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
     const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(kThreads), kSmemBytes2, stream, ma, mb, msa, msb, mo, g, fq);
     g_launches.fetch_add(1);

@@ -261,6 +261,9 @@ int ck_b200_read_device_status(int* status_out);
                                              in one launch (default 120: what stays in the 126 MB L2) */
 #define CK_B200_TUNE_DYNAMIC_SMEM 8 /* non-zero (default): inputs of up to about 32 MB with rows and columns multiples of
                                      128 stay in shared memory between the two phases of ck_b200_quantize_nvfp4_dynamic */
+#define CK_B200_TUNE_GEMM_MAX_PAIRS 9 /* n > 0: the CTA-pair GEMM (and its all-gather form) launches at most n pairs of CTAs
+                                       instead of one per pair of SMs, so that two such kernels on two streams run side by
+                                       side; 0 (default) = all */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus
