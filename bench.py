@@ -839,6 +839,36 @@ def wan_record(B: Bench, args):
         torch.cuda.empty_cache()
 
 
+def run_kernels_only(args, wl):
+    """A short, fixed sequence of the path's kernels for a profiler to pick launches from (ncu -k ... -s ... -c ...):
+    two rounds over the workload's linears, each round launching per linear the quantizer with the given scale, the
+    one-launch dynamic quantizer and the GEMM.  The first round warms up; nothing is timed."""
+    import torch
+
+    import comfy_kitchen_b200 as ckb
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    xs_cpu, ws_cpu = make_inputs(wl, torch.bfloat16)
+    xs = [x.to(dev) for x in xs_cpu]
+    weights = []
+    for w in ws_cpu:
+        wd = w.to(dev)
+        tw = ckb.dynamic_scale_nvfp4(wd)
+        weights.append(ckb.quantize_nvfp4(wd, tw) + (tw,))
+        del wd
+    ts = [ckb.dynamic_scale_nvfp4(x) for x in xs]
+    torch.cuda.synchronize()
+    n0 = ckb.launches()
+    for _ in range(2):
+        for x, t, (wq, wsf, tw) in zip(xs, ts, weights):
+            q, sf = ckb.quantize_nvfp4(x, t)
+            ckb.quantize_nvfp4_dynamic(x)
+            ckb.scaled_mm_nvfp4(q, wq, t, tw, sf, wsf)
+        torch.cuda.synchronize()
+    print(json.dumps({"kernels_only": wl["name"], "launches": ckb.launches() - n0, "device_status": ckb.read_device_status(),
+                      "order_per_round": "per linear: quantize_nvfp4, quantize_nvfp4_dynamic, scaled_mm_nvfp4"}), flush=True)
+
+
 def run_ours(args, wl):
     import torch
 
@@ -1234,10 +1264,14 @@ def main():
     ap.add_argument("--e2e-serial", action="store_true",
                     help="end-to-end arm: one host<->device transfer at a time instead of overlapping the two directions")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="launch each kernel of the path twice on the workload's shapes and exit (a target for ncu captures)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, wl)
+    elif args.kernels_only:
+        run_kernels_only(args, wl)
     else:
         run_ours(args, wl)
 
