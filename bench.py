@@ -1093,9 +1093,15 @@ def run_ours(args, wl):
         comparators = quantize_comparators(B, xs, ts_x, [l[0] for l in wl["linears"]])
 
     # ---- end to end: pinned host activations in, host outputs back, copies inside the timed region ----
+    # One GPU: the whole activation comes up, the whole output goes back.  Several GPUs: the job's input still crosses
+    # PCIe once in total - rank r uploads rows [r M/G, (r+1) M/G) of every activation and the ranks all-gather the
+    # slices over NVLink (every rank needs the whole activation for its column block) - and every rank downloads its
+    # own column block of the output.
     x_host = [x.pin_memory() for x in xs_cpu]
     y_host = [torch.empty((M, lin.local_rows), dtype=torch.bfloat16).pin_memory() for lin in layers]
-    h2d = sum(x.numel() * 2 for x in x_host)
+    shard_upload = distributed and M % world == 0
+    r0, r1 = (rank * (M // world), (rank + 1) * (M // world)) if shard_upload else (0, M)
+    h2d = sum((r1 - r0) * x.shape[1] * 2 for x in x_host)
     d2h = sum(y.numel() * 2 for y in y_host)
 
     # Three streams: uploads, the operators (the current stream), downloads.  PCIe carries both directions at once and
@@ -1104,6 +1110,7 @@ def run_ours(args, wl):
     # its own device input buffer, reused every step once the operators of the previous step have read it.
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     x_dev = [torch.empty_like(x) for x in xs]
+    x_part = [torch.empty((r1 - r0, x.shape[1]), dtype=x.dtype, device=dev) for x in xs] if shard_upload else None
     ev_in = [torch.cuda.Event() for _ in layers]
     ev_cmp = [torch.cuda.Event() for _ in layers]
     ev_out = [torch.cuda.Event() for _ in layers]
@@ -1113,13 +1120,18 @@ def run_ours(args, wl):
     def e2e_step():
         cur = torch.cuda.current_stream()
         for i, (xh, yh, lin) in enumerate(zip(x_host, y_host, layers)):
-            s_in.wait_event(ev_cmp[i])                     # last step's operators are done with x_dev[i]
+            s_in.wait_event(ev_cmp[i])                     # last step's operators are done with x_dev[i] / x_part[i]
             if serial:
                 s_in.wait_stream(s_out)
             with torch.cuda.stream(s_in):
-                x_dev[i].copy_(xh, non_blocking=True)
+                if shard_upload:
+                    x_part[i].copy_(xh[r0:r1], non_blocking=True)
+                else:
+                    x_dev[i].copy_(xh, non_blocking=True)
                 ev_in[i].record()
             cur.wait_event(ev_in[i])
+            if shard_upload:
+                dist.all_gather_into_tensor(x_dev[i], x_part[i])      # rows of all ranks, in rank order, over NVLink
             if fused:
                 cur.wait_event(ev_out[i])                  # last step's download has read this rank's matrix
                 peers.barrier()
@@ -1146,8 +1158,11 @@ def run_ours(args, wl):
     e2e = {"value": fl * args.steps / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": ems / args.steps,
            "pcie_gbs": {"h2d": h2d / (ems / args.steps * 1e-3) / 1e9, "d2h": d2h / (ems / args.steps * 1e-3) / 1e9},
+           "h2d_bytes_per_step_all_ranks": h2d * world, "d2h_bytes_per_step_all_ranks": d2h * world,
            "what": "pinned host bf16 activations -> device, quantize_nvfp4 + scaled_mm_nvfp4 through the operator "
-                   "interface, bf16 outputs -> pinned host; per rank; "
+                   "interface, bf16 outputs -> pinned host; bytes per rank; "
+                   + ("each rank uploads its M/G rows of every activation and the ranks all-gather them over NVLink, "
+                      "each downloads its own column block; " if shard_upload else "")
                    + ("one transfer at a time" if serial else
                       "uploads, operators and downloads on three streams, so the two PCIe directions overlap")}
     if args.gemm_debug and rank == 0:

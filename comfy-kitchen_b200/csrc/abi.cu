@@ -16,7 +16,7 @@ std::atomic<int> g_gemm_max_pairs{0};
 std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
-std::atomic<int> g_dynamic_fused_max_mb{120};
+std::atomic<int> g_dynamic_fused_max_mb{64};
 std::atomic<int> g_dynamic_smem{1};
 
 char* last_error_buffer() {
