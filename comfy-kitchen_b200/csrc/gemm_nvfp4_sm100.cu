@@ -1426,11 +1426,21 @@ int launch_gemm_pair(const void* a, const void* b, GemmArgs g, int64_t K, cudaSt
         if (!fused) return fail(CK_B200_ERR_INVALID_ARGUMENT, "fused quantizer: missing description");
         fq = *fused;
     }
-    if (g.debug) {   // the regular build was opted in to its shared memory by max_active_pairs, once per device
-        cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
-        if (attr_err != cudaSuccess)
-            return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
-                        cudaGetErrorString(attr_err));
+    {
+        // opting in to large dynamic shared memory is per function (this template instance, with or without counters)
+        // and per device: once
+        static std::mutex mu;
+        static bool done[2][64] = {};
+        int dev = 0;
+        CKB_CUDA_OK(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !done[g.debug ? 1 : 0][dev]) {
+            cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+            if (attr_err != cudaSuccess)
+                return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", kSmemBytes2,
+                            cudaGetErrorString(attr_err));
+            if (dev >= 0 && dev < 64) done[g.debug ? 1 : 0][dev] = true;
+        }
     }
     CUtensorMap ma, mb, msa, msb, mo;
     if (int rc = make_operand_map(&ma, a, g.M, row_bytes, BM, KB)) return rc;
