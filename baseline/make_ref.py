@@ -25,7 +25,9 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
-DEFAULT_CHECKOUT = "/root/reference"
+# the reference checkout: $COMFY_KITCHEN_REFERENCE, else a directory named "reference" beside this repository
+DEFAULT_CHECKOUT = os.environ.get("COMFY_KITCHEN_REFERENCE",
+                                  os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 REF_TESTS = ["__init__.py", "conftest.py", "test_qdq.py", "test_tensor.py", "test_integration.py"]
 
 

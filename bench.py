@@ -753,6 +753,34 @@ def small_m_sweep(B: Bench):
     return small_m
 
 
+def eager_latency(B: Bench):
+    """Wall-clock time per forward of a 4096 -> 4096 NVFP4 layer called eagerly (no CUDA graph), dynamic activation
+    scale, as the reference layer is used (samples/nvfp4_linear.py:77-80): host work (Python, ctypes, tensor-map
+    encoding, launches) plus device work, averaged over 200 back-to-back calls followed by one synchronise."""
+    import comfy_kitchen_b200 as ckb
+    torch = B.torch
+    g = torch.Generator(device=B.dev).manual_seed(11)
+    w = (torch.randn((4096, 4096), generator=g, device=B.dev) * 0.02).to(torch.bfloat16)
+    lin = ckb.NVFP4Linear.from_float(w, None)
+    out = []
+    for m in (1, 64, 512):
+        x = torch.randn((m, 4096), generator=g, device=B.dev, dtype=torch.bfloat16)
+        rec = {"M": m}
+        for name, f in (("one_call_us", lin.forward), ("three_operators_us", lin.forward_unfused)):
+            for _ in range(20):
+                f(x)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(200):
+                f(x)
+            torch.cuda.synchronize()
+            rec[name] = (time.perf_counter() - t0) / 200 * 1e6
+        out.append(rec)
+    return {"layer": "NVFP4Linear 4096 -> 4096, bf16, input_scale=None", "per_forward": out,
+            "one_call": "ck_b200_linear_nvfp4 (dynamic quantizer, GEMM: 2-3 launches from one library call)",
+            "three_operators": "dynamic_scale_nvfp4, quantize_nvfp4, scaled_mm_nvfp4 (5-6 launches from three calls)"}
+
+
 def mxfp8_record(B: Bench, wl, xs, ws_cpu, steps):
     """The MXFP8 sibling path on the same workload: quantizer GB/s (3.03125 algorithmic bytes per element: 2 in, 1 out,
     1/32 scale) and GEMM TFLOP/s per linear, with cuBLASLt's MXFP8 kernel beside it."""
@@ -1085,10 +1113,11 @@ def run_ours(args, wl):
         "per_linear": per_linear,
     }
 
-    sweep = small_m = mxfp8 = comparators = None
+    sweep = small_m = mxfp8 = comparators = eager = None
     if not distributed and not args.no_sweep:
         sweep = quantize_sweep(B)
         small_m = small_m_sweep(B)
+        eager = eager_latency(B)
         mxfp8 = mxfp8_record(B, wl, xs, ws_cpu, args.steps)
         comparators = quantize_comparators(B, xs, ts_x, [l[0] for l in wl["linears"]])
 
@@ -1234,7 +1263,8 @@ def run_ours(args, wl):
             "parity": parity, "sustained": sustained, "serial_chain": serial_chain, "dynamic_scale_step": dynamic,
             "fp4_ceiling": ceiling, "cublaslt_comparator": cublaslt, "device_status": status,
             "quantize_gbs": quant_gbs, "quantize_row_sharded": row_sharded, "gemm_only_tflops": gemm_tflops,
-            "quantize_sweep": sweep, "quantize_comparators": comparators, "small_m_sweep": small_m, "mxfp8": mxfp8,
+            "quantize_sweep": sweep, "quantize_comparators": comparators, "small_m_sweep": small_m,
+            "eager_latency": eager, "mxfp8": mxfp8,
             "fused_linear": fused_linear, "wan": wan,
         }
         if nvlink is not None:

@@ -7,6 +7,7 @@ handling only; the arithmetic runs in the kernels of ``libck_b200.so``.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -38,6 +39,18 @@ def _workspace(device: torch.device) -> torch.Tensor | None:
         ws = torch.empty(_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
     return ws
+
+
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _on_device(device: torch.device):
+    """Device guard for the calls below; free when ``device`` already is the current device (the usual case), where
+    torch's guard object would cost several microseconds per operator call."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 def roundup(x: int, multiple: int) -> int:
@@ -90,7 +103,7 @@ def quantize_nvfp4(x: torch.Tensor, per_tensor_scale: torch.Tensor, epsilon: flo
         num_rows, num_cols = orig_rows, orig_cols
         assert num_rows % 16 == 0, f"num_rows must be divisible by 16, got {num_rows}"
         assert num_cols % 16 == 0, f"num_cols must be divisible by 16, got {num_cols}"
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         pts = _scale_on(x.device, per_tensor_scale)
         qx = torch.empty((num_rows, num_cols // 2), device=x.device, dtype=torch.uint8)
         # the kernel writes every byte of the scale tensor, zero padding included: no memset pass
@@ -139,7 +152,7 @@ def quantize_nvfp4_dynamic(x: torch.Tensor, pad_16x: bool = False, hi_first: boo
         num_rows, num_cols = orig_rows, orig_cols
         assert num_rows % 16 == 0, f"num_rows must be divisible by 16, got {num_rows}"
         assert num_cols % 16 == 0, f"num_cols must be divisible by 16, got {num_cols}"
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         scale = torch.empty((), device=x.device, dtype=torch.float32)
         qx = torch.empty((num_rows, num_cols // 2), device=x.device, dtype=torch.uint8)
         sx = torch.empty((roundup(num_rows, 128), roundup(num_cols // 16, 4)), device=x.device, dtype=torch.uint8)
@@ -167,7 +180,7 @@ def dequantize_nvfp4(qx: torch.Tensor, per_tensor_scale: torch.Tensor, block_sca
     if block_scales.numel() != want[0] * want[1] or block_scales.element_size() != 1:
         raise ValueError(f"block_scales must hold {want[0]}x{want[1]} one-byte scales, got {tuple(block_scales.shape)}")
     assert block_scales.is_contiguous() and block_scales.device == qx.device
-    with torch.cuda.device(qx.device):
+    with _on_device(qx.device):
         pts = _scale_on(qx.device, per_tensor_scale)
         out = torch.empty((num_rows, packed * 2), device=qx.device, dtype=output_type)
         if out.numel() == 0:
@@ -217,7 +230,7 @@ def scaled_mm_nvfp4(a: torch.Tensor, b: torch.Tensor, tensor_scale_a: torch.Tens
         bias_code = DTYPE_TO_CODE[bias.dtype]
     else:
         bias = None
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         alpha_t = None
         tsa = tsb = None
         if alpha is not None:
@@ -269,7 +282,7 @@ def scaled_mm_nvfp4_all_gather(a: torch.Tensor, b: torch.Tensor, tensor_scale_a:
         bias_code = DTYPE_TO_CODE[bias.dtype]
     world = len(out_ptrs)
     arr = (ctypes.c_void_p * world)(*out_ptrs)
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         tsa = _scale_on(a.device, tensor_scale_a)
         tsb = _scale_on(a.device, tensor_scale_b)
         rc = _lib.load().ck_b200_scaled_mm_nvfp4_all_gather(_ptr(a), _ptr(block_scale_a), _ptr(b), _ptr(block_scale_b),
@@ -284,7 +297,7 @@ def peer_barrier(flag_ptrs: list[int], rank: int, epoch: torch.Tensor) -> None:
     as mapped here; ``epoch``: this rank's zero-initialised int32 counter)."""
     world = len(flag_ptrs)
     arr = (ctypes.c_void_p * world)(*flag_ptrs)
-    with torch.cuda.device(epoch.device):
+    with _on_device(epoch.device):
         rc = _lib.load().ck_b200_peer_barrier(arr, world, rank, _ptr(epoch), _stream(epoch.device))
     _lib.check(rc, "peer_barrier")
 
@@ -293,25 +306,25 @@ def peer_alloc(nbytes: int, device: torch.device) -> tuple[int, bytes]:
     """Zeroed device memory other processes of the node can map: (address, 64-byte handle)."""
     ptr = ctypes.c_void_p()
     handle = ctypes.create_string_buffer(64)
-    with torch.cuda.device(device):
+    with _on_device(device):
         _lib.check(_lib.load().ck_b200_peer_alloc(nbytes, ctypes.byref(ptr), handle), "peer_alloc")
     return int(ptr.value), handle.raw
 
 
 def peer_open(handle: bytes, device: torch.device) -> int:
     ptr = ctypes.c_void_p()
-    with torch.cuda.device(device):
+    with _on_device(device):
         _lib.check(_lib.load().ck_b200_peer_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(ptr)), "peer_open")
     return int(ptr.value)
 
 
 def peer_close(ptr: int, device: torch.device) -> None:
-    with torch.cuda.device(device):
+    with _on_device(device):
         _lib.check(_lib.load().ck_b200_peer_close(ptr), "peer_close")
 
 
 def peer_free(ptr: int, device: torch.device) -> None:
-    with torch.cuda.device(device):
+    with _on_device(device):
         _lib.check(_lib.load().ck_b200_peer_free(ptr), "peer_free")
 
 
@@ -332,7 +345,7 @@ def quantize_mxfp8(x: torch.Tensor, pad_32x: bool = False) -> tuple[torch.Tensor
         prow, pcol = rows, cols
         assert rows % 32 == 0, f"num_rows must be divisible by 32, got {rows}"
         assert cols % 32 == 0, f"num_cols must be divisible by 32, got {cols}"
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         q = torch.empty((prow, pcol), dtype=torch.uint8, device=x.device)
         sf = torch.empty((roundup(prow, 128), roundup(pcol // 32, 4)), dtype=torch.uint8, device=x.device)
         rc = _lib.load().ck_b200_quantize_mxfp8(_ptr(x), DTYPE_TO_CODE[x.dtype], _ptr(q), _ptr(sf), rows, cols,
@@ -349,7 +362,7 @@ def dequantize_mxfp8(qx: torch.Tensor, block_scales: torch.Tensor, output_type: 
     assert qx.dim() == 2 and qx.is_contiguous() and block_scales.is_contiguous()
     rows, cols = qx.shape
     assert tuple(block_scales.shape) == (roundup(rows, 128), roundup(cols // 32, 4)), "Invalid scale shape"
-    with torch.cuda.device(qx.device):
+    with _on_device(qx.device):
         out = torch.empty((rows, cols), dtype=output_type, device=qx.device)
         rc = _lib.load().ck_b200_dequantize_mxfp8(_ptr(qx), _ptr(block_scales), _ptr(out), DTYPE_TO_CODE[output_type],
                                                   rows, cols, _stream(qx.device))
@@ -382,7 +395,7 @@ def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
         bias_code = DTYPE_TO_CODE[bias.dtype]
     else:
         bias = None
-    with torch.cuda.device(a.device):
+    with _on_device(a.device):
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
         if out.numel() == 0:
             return out
@@ -431,7 +444,7 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
     need += _WORKSPACE_BYTES if m <= 128 else 0
     key = _stream_key(x.device)
     ws = _LINEAR_WS.get(key)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         if ws is None or ws.numel() < need:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("linear_nvfp4: the workspace of this stream must grow, which cannot happen inside a "
@@ -461,7 +474,7 @@ def dynamic_scale_nvfp4(x: torch.Tensor) -> torch.Tensor:
     if x.dtype not in DTYPE_TO_CODE:
         raise TypeError(f"dynamic_scale_nvfp4: unsupported dtype {x.dtype}")
     assert x.is_contiguous(), "Input tensor must be contiguous"
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         out = torch.empty((), device=x.device, dtype=torch.float32)
         rc = _lib.load().ck_b200_dynamic_scale_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], x.numel(), _ptr(out),
                                                      _stream(x.device))
