@@ -158,13 +158,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
-// Bring a box of a tensor map, or a plain range, into L2 (this GPU's memory; nothing is handed to the kernel).
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
                  "r"(y), "r"(src)
@@ -372,27 +365,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_items = g.m_tiles * g.n_tiles * g.splits;
-    if (warp == 0 && g.m_tiles == 1 && (int)blockIdx.x < total_items) {
-        // One tile row (M <= 128): the time goes into streaming the weight, which does not depend on the kernel in front of
-        // this one (the activation does).  While that kernel is still finishing, ask for this CTA's first work item's
-        // share of B and of its scales to be brought into L2 - a prefetch hands nothing to this kernel, so the order with
-        // respect to earlier writes is kept by the loads after the wait below, which then find the lines in L2.
-        const int item = blockIdx.x;
-        const int tile = item / g.splits;
-        const int kb0 = (item - tile * g.splits) * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);
-        int tm, tn;
-        tile_coords(g, tile, tm, tn);
-        for (int kb = kb0 + lane; kb < kb1; kb += 32) {
-            tma_prefetch_2d(&tmap_b, kb * BK_BYTES, tn * BN);
-            const int chunk0 = (FMT == 1) ? kb : kb * CHUNKS;
-            const int nchunk = (FMT == 1) ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
-#pragma unroll
-            for (int b = 0; b < C::kBands; ++b)
-                if (tn * C::kBands + b < g.sfb_bands)
-                    bulk_prefetch_l2(g.sfb + (((int64_t)tn * C::kBands + b) * g.sf_cbg + chunk0) * SF_CHUNK_BYTES,
-                                     (uint32_t)(nchunk * SF_CHUNK_BYTES));
-        }
-    }
     grid_dependency_wait();   // barriers and tensor memory are set up while the previous kernel drains
 
     // cycle counters of the debug build (DBG): compiled out otherwise

@@ -83,9 +83,11 @@ class NVFP4Linear(nn.Module):
             bias = torch.nn.functional.pad(bias, (0, self.weight.shape[0] - bias.shape[0]))
         # one library call: activation scale, quantization of x (rows padded to 16) and the GEMM.  The quantized
         # activation sits in a per-device workspace, so calls on one device must be ordered on one stream.
-        y = ops.linear_nvfp4(x2, self.weight, self.weight_scale.view(torch.float8_e4m3fn), self.weight_scale_2,
+        y = ops.linear_nvfp4(x2, self.weight, self.weight_scale, self.weight_scale_2,
                              input_scale=self.input_scale, bias=bias, out_dtype=out_dtype)
-        return y[:, : self.out_features].reshape(*lead, self.out_features)
+        if y.shape[1] != self.out_features:
+            y = y[:, : self.out_features]
+        return y if len(lead) == 1 else y.reshape(*lead, self.out_features)
 
     def forward_unfused(self, x: torch.Tensor) -> torch.Tensor:
         """The same result through the three operators of the reference interface, one call each."""

@@ -77,7 +77,7 @@ def _scale_on(device: torch.device, s: torch.Tensor) -> torch.Tensor:
         raise ValueError("per-tensor scale must have exactly one element")
     if s.device != device:
         s = s.to(device, non_blocking=True)
-    return s.reshape(1) if s.is_contiguous() else s.contiguous().reshape(1)
+    return s      # one element: any view of it is contiguous, and only its address is used
 
 
 def _require_cuda(t: torch.Tensor, name: str) -> None:
@@ -408,6 +408,7 @@ def scaled_mm_mxfp8(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tenso
 
 
 _LINEAR_WS: dict[tuple[int, int], torch.Tensor] = {}
+_LINEAR_NEED: dict[tuple[int, int], int] = {}     # workspace bytes by (M, K)
 
 
 def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: torch.Tensor, weight_scale: torch.Tensor,
@@ -438,11 +439,17 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
         assert bias.numel() == n and bias.is_contiguous() and bias.dtype in (torch.float16, torch.bfloat16)
         bias_code = DTYPE_TO_CODE[bias.dtype]
     L = _lib.load()
-    need = L.ck_b200_linear_nvfp4_workspace_bytes(m, k)
-    if need < 0:
-        raise RuntimeError(f"linear_nvfp4: K = {k} must be a multiple of 32")
-    need += _WORKSPACE_BYTES if m <= 128 else 0
-    key = _stream_key(x.device)
+    need = _LINEAR_NEED.get((m, k))
+    if need is None:
+        need = L.ck_b200_linear_nvfp4_workspace_bytes(m, k)
+        if need < 0:
+            raise RuntimeError(f"linear_nvfp4: K = {k} must be a multiple of 32")
+        need += _WORKSPACE_BYTES if m <= 128 else 0
+        if len(_LINEAR_NEED) < 4096:
+            _LINEAR_NEED[(m, k)] = need
+    dev_index = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    stream = int(torch.cuda.current_stream(x.device).cuda_stream)
+    key = (dev_index, stream)
     ws = _LINEAR_WS.get(key)
     with _on_device(x.device):
         if ws is None or ws.numel() < need:
@@ -460,8 +467,9 @@ def linear_nvfp4(x: torch.Tensor, qweight: torch.Tensor, weight_block_scale: tor
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         rc = L.ck_b200_linear_nvfp4(_ptr(x), DTYPE_TO_CODE[x.dtype], m, k, _ptr(in_ts), _ptr(qweight),
                                     _ptr(weight_block_scale), _ptr(w_ts), n, _ptr(bias), bias_code, _ptr(out),
-                                    DTYPE_TO_CODE[out_dtype], _ptr(ws), ws.numel(), _stream(x.device))
-    _lib.check(rc, "linear_nvfp4")
+                                    DTYPE_TO_CODE[out_dtype], _ptr(ws), ws.numel(), ctypes.c_void_p(stream))
+    if rc:
+        _lib.check(rc, "linear_nvfp4")
     return out
 
 
