@@ -955,6 +955,30 @@ def run_ours(args, wl):
     fl = flops_per_step(wl)
     value = fl * args.steps / (ms * 1e-3) / 1e12
 
+    # the outputs the timed graph itself left behind, against the same linears computed outside it
+    if plan.use_graph and overlap:
+        kept = B.graphs[-1]._keep[0]
+        ok = 1
+        for x, lin, got in zip(xs, layers, kept):
+            want = lin.gather(lin.local(x)) if fused else lin.local(x)
+            if not torch.equal(got, want):
+                ok = 0
+        if distributed:
+            flag = torch.tensor([ok], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = int(flag.item())
+        parity["timed_graph"] = ("outputs of the last timed replay bit-equal to " +
+                                 ("the NCCL all-gather of separately computed blocks" if fused else
+                                  "the same linears launched one after the other")) if ok else "MISMATCH"
+        parity["ok"] = bool(parity.get("ok", True) and ok)
+        if not ok:
+            if rank == 0:
+                print(json.dumps({"error": "parity check of the timed graph failed", "parity": parity}), flush=True)
+            plan.close()
+            if distributed:
+                dist.destroy_process_group()
+            sys.exit(3)
+
     serial_chain = None
     if overlap:
         replay_s, n_s = B.graphed(lambda: plan.step(one_call=one_call), use_graph=plan.use_graph)
