@@ -75,6 +75,22 @@ def _worker(rank, world, port, n_out, result_dir):
             buf = lin.gather(lin.local(x), row_major=False)
             assert tuple(buf.shape) == (world, 48, n_out // world)
             assert torch.equal(buf.permute(1, 0, 2).reshape(48, n_out), y)
+        # the two halves a caller may put on different streams give the block of local()
+        qx2, sfx2, ts2 = lin.quantize_input(x)
+        assert torch.equal(lin.local_from_quantized(qx2, sfx2, ts2, x.shape[0]), lin.local(x))
+        # a dynamic quantizer, where the operator set has one, is what quantize_input uses when no scale is stored
+        calls = []
+
+        def quantize_nvfp4_dynamic(x, pad_16x=False, hi_first=True):
+            calls.append(tuple(x.shape))
+            t = ops.dynamic_scale_nvfp4(x)
+            return ops.quantize_nvfp4(x, t, pad_16x=pad_16x, hi_first=hi_first) + (t,)
+
+        ops2 = SimpleNamespace(**vars(ops), quantize_nvfp4_dynamic=quantize_nvfp4_dynamic)
+        lin2 = ckb.ShardedNVFP4Linear(w, bias, ops=ops2)
+        assert torch.equal(lin2(x), y) and calls == [(48, 128)]
+        lin3 = ckb.ShardedNVFP4Linear(w, bias, ops=ops2, input_scale=ops.dynamic_scale_nvfp4(x))
+        assert torch.equal(lin3(x), y) and len(calls) == 1     # a stored scale is used as it is
         np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([1]))
     finally:
         dist.destroy_process_group()
