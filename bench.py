@@ -1317,7 +1317,7 @@ def main():
                     help="time the eight kernels of a step as one chain instead of overlapping each quantizer with the "
                          "previous linear's GEMM")
     ap.add_argument("--sustained-seconds", type=float, default=3.0)
-    ap.add_argument("--peer-map-limit-gib", type=int, default=64,
+    ap.add_argument("--peer-map-limit-gib", type=int, default=12,
                     help="N > 1: above this many GiB of peer-mapped output matrices per rank the NCCL all-gather is used")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic stream serialisation")
