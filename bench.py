@@ -1013,7 +1013,24 @@ def run_ours(args, wl):
         ms_s, reps_s = B.for_seconds(replay_step, args.sustained_seconds, 200)
         c2 = s2.stop()
         v = fl * reps_s / (ms_s * 1e-3) / 1e12
+        # right after the loop, while the GPU is at its sustained operating point: one launch per linear of the GEMM build
+        # with cycle counters (CTA pair 0 reports cycles and nanoseconds of its epilogue role: the SM clock inside the
+        # kernel, and the share of its time the MMA role spent waiting)
+        in_kernel = {}
+        qx_s = [lin.quantize_input(x) for x, lin in zip(xs, layers)]
+        try:
+            for (name, _, _), (q, sf, t), lin in zip(wl["linears"], qx_s, layers):
+                ckb.set_tuning(2, 0)
+                for _ in range(20):
+                    lin.local_from_quantized(q, sf, t, M)          # keep the load on
+                ckb.set_tuning(2, 2)                               # counting build, counters only (1 would also print)
+                lin.local_from_quantized(q, sf, t, M)
+                in_kernel[name] = ckb.read_gemm_counters()
+        finally:
+            ckb.set_tuning(2, 0)
+        del qx_s
         sustained = {"seconds": ms_s / 1e3, "steps": reps_s, "ms_per_step": ms_s / reps_s, "value": v, "unit": "TFLOP/s",
+                     "in_kernel": in_kernel,
                      "sm_mhz_median": c2.get("sm_mhz"), "sm_mhz_min": c2.get("sm_min_mhz"), "sm_max_mhz": c2.get("sm_max_mhz"),
                      "power_w_median": c2.get("power_w_median"), "power_w_max": c2.get("power_w_max"),
                      "reasons": c2.get("reasons"),

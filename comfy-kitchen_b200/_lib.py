@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "ck_b200_last_error",
     "ck_b200_query",
     "ck_b200_read_device_status",
+    "ck_b200_read_gemm_counters",
     "ck_b200_set_tuning",
 )
 
@@ -95,6 +96,8 @@ def load() -> ctypes.CDLL:
     L.ck_b200_query.restype = i64
     L.ck_b200_read_device_status.argtypes = [ctypes.POINTER(i32)]
     L.ck_b200_read_device_status.restype = i32
+    L.ck_b200_read_gemm_counters.argtypes = [ctypes.POINTER(ctypes.c_longlong)]
+    L.ck_b200_read_gemm_counters.restype = i32
     L.ck_b200_set_tuning.argtypes = [i32, i32]
     L.ck_b200_set_tuning.restype = i32
     _lib = L

@@ -43,6 +43,10 @@ namespace ckb {
 namespace {
 
 __device__ int g_device_status = 0;
+// What the counting build of the CTA-pair kernel last measured: {cycles, nanoseconds} of CTA 0's epilogue role (its
+// ratio is the SM clock inside the kernel), cycles the MMA role waited for loaded stages and for an accumulator, and
+// the MMA role's total.
+__device__ long long g_gemm_counters[5] = {0, 0, 0, 0, 0};
 
 constexpr int BM = 128;             // rows of A per tile = tensor-memory lanes
 constexpr int BK_BYTES = 128;       // packed bytes of K per stage = 256 elements = one swizzle row
@@ -414,7 +418,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (++stage == C::kStages) { stage = 0; phase ^= 1; }
             }
         }
-        if (DBG && blockIdx.x == 0 && lane == 0)
+        if (DBG && g.debug == 1 && blockIdx.x == 0 && lane == 0)
             printf("[gemm bn%d cta0] producer: total %lld cycles, waiting for free stages %lld\n", BN, now() - t_begin,
                    waited);
     } else if (warp == 1) {
@@ -507,7 +511,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
-        if (DBG && blockIdx.x == 0 && lane == 0)
+        if (DBG && g.debug == 1 && blockIdx.x == 0 && lane == 0)
             printf("[gemm bn%d cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", BN,
                    now() - t_begin, wait_acc, wait_full);
     } else {
@@ -609,7 +613,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (acc == 0) acc_phase ^= 1;
         }
         if (g.tma_store && lane == 0) tma_store_wait_all();   // global writes complete before the CTA exits
-        if (DBG && blockIdx.x == 0 && threadIdx.x == 64)
+        if (DBG && g.debug == 1 && blockIdx.x == 0 && threadIdx.x == 64)
             printf("[gemm bn%d cta0] epilogue: total %lld cycles, waiting for accumulators %lld\n", BN, now() - t_begin,
                    wait_acc);
     }
@@ -908,7 +912,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 if (++stage == kStages2) { stage = 0; phase ^= 1; }
             }
         }
-        if (DBG && pair == 0 && lane == 0)
+        if (DBG && g.debug == 1 && pair == 0 && lane == 0)
             printf("[gemm pair cta%u] producer: total %lld cycles, waiting for free stages %lld, for quantized bands %lld\n",
                    rank, now() - t_begin, waited, q_waited);
     } else if (warp == 1 && rank == 0) {
@@ -1000,9 +1004,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
-        if (DBG && pair == 0 && lane == 0)
-            printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n",
-                   now() - t_begin, wait_acc, wait_full);
+        if (DBG && pair == 0 && lane == 0) {
+            const long long cyc = now() - t_begin;
+            if (g.debug == 1) printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", cyc,
+                   wait_acc, wait_full);
+            g_gemm_counters[2] = wait_full;
+            g_gemm_counters[3] = wait_acc;
+            g_gemm_counters[4] = cyc;
+        }
     } else if (QF && warp >= NUM_THREADS / 32) {
         // ---------------- activation quantizer (eight warps of both CTAs) ----------------
         if constexpr (QF) {
@@ -1023,7 +1032,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     if (atomicAdd(&fq.sync->band[band], 1u) + 1u == (uint32_t)per_band) atomicAdd(&fq.sync->bands_done, 1u);
                 }
             }
-            if (DBG && pair == 0 && threadIdx.x == NUM_THREADS)
+            if (DBG && g.debug == 1 && pair == 0 && threadIdx.x == NUM_THREADS)
                 printf("[gemm pair cta%u] quantizer: total %lld cycles\n", rank, now() - t_begin);
         }
     } else if (warp >= 2) {
@@ -1168,9 +1177,15 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         if constexpr (GATHER) bulk_wait_all();   // every copy has been performed before the CTA exits
         else if (g.tma_store && lane == 0) tma_store_wait_all();
-        if (DBG && pair == 0 && threadIdx.x == 64)
-            printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank,
-                   now() - t_begin, now_ns() - t_begin_ns, wait_acc);
+        if (DBG && pair == 0 && threadIdx.x == 64) {
+            const long long cyc = now() - t_begin, ns = now_ns() - t_begin_ns;
+            if (g.debug == 1) printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank, cyc,
+                   ns, wait_acc);
+            if (rank == 0) {
+                g_gemm_counters[0] = cyc;
+                g_gemm_counters[1] = ns;
+            }
+        }
     }
 
     tc_fence_before();
@@ -1904,6 +1919,14 @@ extern "C" int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const v
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
                           bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K,
                           scratch_from_workspace(scratch, kStaticScratchBytes), stream);
+}
+
+extern "C" int ck_b200_read_gemm_counters(long long* out5) {
+    if (int rc = check_device(nullptr)) return rc;
+    if (!out5) return fail(CK_B200_ERR_INVALID_ARGUMENT, "read_gemm_counters: null pointer");
+    CKB_CUDA_OK(cudaDeviceSynchronize());
+    CKB_CUDA_OK(cudaMemcpyFromSymbol(out5, g_gemm_counters, 5 * sizeof(long long)));
+    return CK_B200_OK;
 }
 
 extern "C" int ck_b200_read_device_status(int* status_out) {

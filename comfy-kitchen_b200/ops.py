@@ -499,6 +499,16 @@ def launches() -> int:
     return int(_lib.load().ck_b200_query(_lib.QUERY_LAUNCHES))
 
 
+def read_gemm_counters() -> dict:
+    """Cycle counters of the most recent launch of the counting GEMM build (``set_tuning(2, 1)``), CTA pair 0."""
+    buf = (ctypes.c_longlong * 5)()
+    _lib.check(_lib.load().ck_b200_read_gemm_counters(buf), "read_gemm_counters")
+    cyc, ns, wait_full, wait_acc, mma = (int(v) for v in buf)
+    return {"epilogue_cycles": cyc, "epilogue_ns": ns, "sm_clock_mhz": (cyc / ns * 1e3) if ns > 0 else None,
+            "mma_cycles": mma, "mma_wait_loaded_stages_frac": (wait_full / mma) if mma > 0 else None,
+            "mma_wait_accumulator_frac": (wait_acc / mma) if mma > 0 else None}
+
+
 def read_device_status() -> int:
     """Synchronises and returns the device status word (0 = no bounded wait ran out), clearing it."""
     v = ctypes.c_int(0)

@@ -243,12 +243,22 @@ int64_t ck_b200_query(int what);
  */
 int ck_b200_read_device_status(int* status_out);
 
+/*
+ * What the counting build of the CTA-pair GEMM (CK_B200_TUNE_GEMM_DEBUG = 1) measured in its most recent launch on the
+ * current device, for CTA pair 0: out5[0] cycles and out5[1] nanoseconds of the epilogue role (their ratio is the SM
+ * clock inside the kernel, which NVML's samples do not resolve), out5[2] cycles the MMA role waited for loaded stages,
+ * out5[3] cycles it waited for an accumulator, out5[4] the MMA role's total cycles.  Synchronises the device; for
+ * benchmarks.  No counterpart in the reference (its GEMM is a library call).
+ */
+int ck_b200_read_gemm_counters(long long* out5);
+
 /* Tuning switches used by tests and benchmarks to select kernel variants: key/value integers,
  * returns the previous value or -1 for an unknown key.  No counterpart in the reference (its
  * environment switches, comfy_kitchen/backends/cuda/__init__.py:212-215, do not touch this path). */
 #define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions, 1 = reciprocal bracket + exact fallback, 2 = one-round residual correction (default) */
 #define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic */
-#define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the GEMM kernel's first CTA prints the cycles its roles spent waiting */
+#define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the counting build of the GEMM kernels runs; 1 = its first CTA also prints the
+                                        cycles its roles spent waiting, 2 = counters only (ck_b200_read_gemm_counters) */
 #define CK_B200_TUNE_DEPENDENT_LAUNCH 3 /* non-zero (default): kernels are launched with programmatic stream
                                           serialisation, so a kernel's set-up overlaps the previous kernel's tail */
 #define CK_B200_TUNE_LINEAR_FUSED 4  /* non-zero: ck_b200_linear_nvfp4 quantizes the activations inside the GEMM kernel
