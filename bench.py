@@ -1078,11 +1078,17 @@ def run_ours(args, wl):
         rq, _ = B.graphed(repeated(one_quant(i)))
         tg = B.timed(rg, args.steps) / (args.steps * R)
         tq = B.timed(rq, args.steps) / (args.steps * R)
+        # the same quantizer launch through the register-ring kernels (inputs of up to ~32 MB otherwise go through
+        # shared memory with the whole input in flight)
+        prev_onchip = ckb.set_tuning(10, 0)
+        rq2, _ = B.graphed(repeated(one_quant(i)))
+        tq_ring = B.timed(rq2, args.steps) / (args.steps * R)
+        ckb.set_tuning(10, prev_onchip)
         B.graphs.clear()
         n_local = lin.local_rows
         per_linear.append({"linear": name, "K": k, "N_local": n_local, "quantize_us": tq * 1e3, "gemm_us": tg * 1e3,
                            "gemm_tflops": 2.0 * M * n_local * k / (tg * 1e-3) / 1e12,
-                           "quantize_gbs": M * k * 2.5625 / (tq * 1e-3) / 1e9})
+                           "quantize_gbs": M * k * 2.5625 / (tq * 1e-3) / 1e9, "quantize_ring_kernels_us": tq_ring * 1e3})
         gemm_ms += tg
         quant_ms += tq
         gemm_fl += 2.0 * M * n_local * k

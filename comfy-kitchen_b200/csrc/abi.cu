@@ -18,6 +18,7 @@ std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
 std::atomic<int> g_dynamic_fused_max_mb{64};
 std::atomic<int> g_dynamic_smem{1};
+std::atomic<int> g_quant_onchip{1};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};
@@ -105,6 +106,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB: return ckb::g_dynamic_fused_max_mb.exchange(value);
         case CK_B200_TUNE_DYNAMIC_SMEM: return ckb::g_dynamic_smem.exchange(value);
         case CK_B200_TUNE_GEMM_MAX_PAIRS: return ckb::g_gemm_max_pairs.exchange(value);
+        case CK_B200_TUNE_QUANT_ONCHIP: return ckb::g_quant_onchip.exchange(value);
         default: return -1;
     }
 }

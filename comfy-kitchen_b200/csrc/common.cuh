@@ -35,6 +35,7 @@ int check_device(int* sm_count_out);
 extern std::atomic<int> g_linear_fused;
 extern std::atomic<int> g_quant_flat;   // 0 = off, else the least units per warp for the one-wave quantizer geometry
 extern std::atomic<int> g_quant_sync_test;       // > 0: the dynamic quantizer expects that many arrivals too many (tests)
+extern std::atomic<int> g_quant_onchip;           // non-zero: inputs that fit the SMs' shared memory are quantized from there
 extern std::atomic<int> g_dynamic_smem;           // non-zero: small inputs are parked in shared memory between the two phases
 extern std::atomic<int> g_dynamic_fused_max_mb;  // largest input (10^6 bytes) the dynamic quantizer handles in one launch
 // Status word of the quantizer kernels (its own translation unit): reads and clears it.

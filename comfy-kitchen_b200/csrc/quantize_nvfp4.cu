@@ -69,9 +69,19 @@ cudaError_t launch_quantize_flat(const QuantArgs& a, int resident_warps, cudaStr
                             dim3(32, kWarpsPerBlock), 0, stream, a, per_warp, total);
 }
 
+// Inputs of up to about 32 MB with rows and columns multiples of 128: the whole input in flight at once, parked in
+// shared memory (quantize_nvfp4_onchip_kernel, defined with the dynamic quantizer below).  Sets *launched.
+template <int DT>
+int launch_quantize_onchip(const QuantArgs& a, int sms, cudaStream_t stream, bool* launched);
+
 template <int DT>
 int launch_quantize(QuantArgs a, bool vec, int variant, int sms, cudaStream_t stream) {
     if (a.row_groups <= 0 || a.sf_cbg <= 0) return CK_B200_OK;
+    if (vec && variant == 2 && g_quant_onchip.load()) {
+        bool launched = false;
+        if (int rc = launch_quantize_onchip<DT>(a, sms, stream, &launched)) return rc;
+        if (launched) return CK_B200_OK;
+    }
     {
         // one wave of long walks once every resident warp gets at least `kFlatMinUnits` units; rows with an odd
         // number of units stay on the segment geometry (ranges would start on odd units)
@@ -440,14 +450,49 @@ quantize_nvfp4_dynamic_kernel(const QuantArgs a, float* __restrict__ scale_out, 
 }
 
 
-// The same for activations small enough to be held on chip between the two phases (up to about 32 MB of 16-bit
-// input: 18 units per warp, 72 KB of shared memory per block, three blocks per SM): phase 1 parks each warp's range in
-// shared memory while taking the maximum, phase 2 quantizes from there, so x is read from HBM once and from nowhere
-// else.  Interior shapes only (rows and columns multiples of 128: no padding rows, whole pairs of units).
-template <int DT>
+// ---- inputs that fit the SMs' shared memory: the whole input in flight at once ------------------------------------
+//
+// Up to about 32 MB of 16-bit input (18 units per warp, 72 KB of shared memory per block, three blocks per SM - the
+// 28 MB activation of a Flux-class block is exactly this size) every warp asks for its whole range at once with
+// 16-byte asynchronous copies into shared memory (no registers held, so nothing limits how much is in flight), one
+// copy group per pair of units, and quantizes pair after pair as the groups land.  A register ring over the same range
+// needs three rounds of HBM latency (6 + 6 + 4 units); this needs one, which is what a 9 us kernel is made of.
+// Interior shapes only (rows and columns multiples of 128: no padding rows, whole pairs of units).
+// DYNAMIC: the per-tensor scale is derived from the input itself (the layout's amax / (448 * 6)): the maximum is
+// taken over the parked range, the blocks meet at the grid-wide counter, and the parked range is quantized with the
+// scale all blocks agree on - x is read from HBM once and from nowhere else.
+constexpr int kOnchipMaxUnits = 18;   // units per warp that can be parked (72 KB per block)
+constexpr int kOnchipMaxPairs = kOnchipMaxUnits / 2;
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Every warp commits kOnchipMaxPairs groups (empty ones at the end): group `pair` has landed once at most
+// kOnchipMaxPairs - 1 - pair younger groups are pending.
+__device__ __forceinline__ void cp_async_wait_pair(int pair) {
+    switch (pair) {
+        case 0: cp_async_wait<8>(); break;
+        case 1: cp_async_wait<7>(); break;
+        case 2: cp_async_wait<6>(); break;
+        case 3: cp_async_wait<5>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<3>(); break;
+        case 6: cp_async_wait<2>(); break;
+        case 7: cp_async_wait<1>(); break;
+        default: cp_async_wait<0>(); break;
+    }
+}
+static_assert(kOnchipMaxPairs == 9, "cp_async_wait_pair covers nine groups");
+
+template <int DT, bool DYNAMIC>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, kBlocksPerSM)
-quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_out, DynamicSync* __restrict__ sync, int per_warp,
-                                   long long total_units, unsigned expected_blocks, long long wait_cycles) {
+quantize_nvfp4_onchip_kernel(const QuantArgs a, float* __restrict__ scale_out, DynamicSync* __restrict__ sync, int per_warp,
+                             long long total_units, unsigned expected_blocks, long long wait_cycles) {
     using In = Input<DT>;
     using Raw = typename In::Raw;
     static_assert(In::kBytes == 2, "16-bit inputs");
@@ -458,15 +503,15 @@ quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_
     __shared__ float s_ts;
     const int lane = threadIdx.x, warp = threadIdx.y;
     uint4* stash = stash_all + (size_t)warp * per_warp * 32 + lane;   // [unit of the range][lane]
+    const uint32_t stash_u32 = smem_u32(stash);
     const long long pos = ((long long)blockIdx.x * kWarpsPerBlock + warp) * per_warp;
     const long long end = min(total_units, pos + per_warp);
     const int sub = lane & 7;
     grid_dependency_wait();
-    // phase 1: park the range in shared memory, eight loads in flight per lane, and take its maximum
-    float m = 0.0f;
+    // phase 1: ask for the whole range
+    int npairs = 0;
     {
         long long p = pos;
-        int j = 0;
         while (p < end) {
             const int gi = (int)(p / a.sf_cbg);
             const int u0 = (int)(p - (long long)gi * a.sf_cbg);
@@ -474,39 +519,42 @@ quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_
             const int group = a.row_groups - 1 - gi;
             const int r = (group >> 5) * 128 + (group & 31) + 32 * (lane >> 3);
             const char* src = (const char*)a.x + ((int64_t)r * a.cols + u0 * 64 + sub * 8) * In::kBytes;
-            int n = u1 - u0;
-            while (n > 0) {
-                Raw v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (i < n) v[i] = In::load_vec(src + i * kUnitBytes);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (i < n) {
-                        stash[(j + i) * 32] = v[i].v;
-                        m = fmaxf(m, raw_amax<DT>(v[i]));
-                    }
-                src += 8 * kUnitBytes;
-                j += n < 8 ? n : 8;
-                n -= 8;
+            for (int u = u0; u < u1; u += 2, ++npairs, src += 2 * kUnitBytes) {
+                cp_async_16(stash_u32 + (uint32_t)(2 * npairs) * 512u, src);
+                cp_async_16(stash_u32 + (uint32_t)(2 * npairs + 1) * 512u, src + kUnitBytes);
+                cp_async_commit();
             }
             p += u1 - u0;
         }
+        for (int k = npairs; k < kOnchipMaxPairs; ++k) cp_async_commit();
     }
+    float ts;
+    if constexpr (DYNAMIC) {
+        cp_async_wait<0>();
+        float m = 0.0f;
+        for (int j = 0; j < 2 * npairs; ++j) {
+            Raw v;
+            v.v = stash[j * 32];
+            m = fmaxf(m, raw_amax<DT>(v));
+        }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) s_max[warp] = m;
-    __syncthreads();
-    if (warp == 0 && lane == 0) {
-        float bm = s_max[0];
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) s_max[warp] = m;
+        __syncthreads();
+        if (warp == 0 && lane == 0) {
+            float bm = s_max[0];
 #pragma unroll
-        for (int w = 1; w < kWarpsPerBlock; ++w) bm = fmaxf(bm, s_max[w]);
-        s_ts = grid_meet<DT>(sync, bm, expected_blocks, wait_cycles, scale_out);
+            for (int w = 1; w < kWarpsPerBlock; ++w) bm = fmaxf(bm, s_max[w]);
+            s_ts = grid_meet<DT>(sync, bm, expected_blocks, wait_cycles, scale_out);
+        }
+        __syncthreads();
+        ts = s_ts;
+        if (ts < 0.0f) return;
+    } else {
+        ts = __ldg(a.pts);
     }
-    __syncthreads();
-    const float ts = s_ts;
-    if (ts < 0.0f || pos >= end) return;
-    // phase 2: quantize the parked range (each lane reads back only what it parked itself)
+    if (pos >= end) return;
+    // phase 2: quantize the parked range pair by pair (each lane reads back only what it asked for itself)
     LaneCtx c;
     c.sub = sub;
     c.odd = sub & 1;
@@ -519,7 +567,7 @@ quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_
     c.pcol = a.pcol;
     const int x_unit = c.odd ? 1 : 0, y_unit = 1 - x_unit;
     long long p = pos;
-    int j = 0;
+    int pair = 0;
     while (p < end) {
         const int gi = (int)(p / a.sf_cbg);
         const int u0 = (int)(p - (long long)gi * a.sf_cbg);
@@ -529,10 +577,11 @@ quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_
         const int r = band * 128 + d3 + 32 * d4;
         uint8_t* q_row = a.q + (int64_t)r * (a.pcol >> 1) + sub * 4;
         uint8_t* sf_row = a.sf + (((int64_t)band * a.sf_cbg) * 32 + d3) * 16 + d4 * 4 + (int64_t)(sub & 1) * 512;
-        for (int u = u0; u < u1; u += 2, j += 2) {
+        for (int u = u0; u < u1; u += 2, ++pair) {
+            if constexpr (!DYNAMIC) cp_async_wait_pair(pair);
             Raw raw_x, raw_y;
-            raw_x.v = stash[(j + x_unit) * 32];
-            raw_y.v = stash[(j + y_unit) * 32];
+            raw_x.v = stash[(2 * pair + x_unit) * 32];
+            raw_y.v = stash[(2 * pair + y_unit) * 32];
             uint32_t wx, wy, s8;
             if (c.hi_first) quantize_pair_xy<DT, true>(c, raw_x, raw_y, wx, wy, s8);
             else quantize_pair_xy<DT, false>(c, raw_x, raw_y, wx, wy, s8);
@@ -545,7 +594,6 @@ quantize_nvfp4_dynamic_smem_kernel(const QuantArgs a, float* __restrict__ scale_
     }
 }
 
-constexpr int kDynamicSmemMaxUnits = 18;   // units per warp the shared-memory variant can park (72 KB per block)
 
 // Resident blocks of the dynamic kernel per SM (cached per device and dtype); never more than kBlocksPerSM.
 template <int DT>
@@ -567,9 +615,9 @@ int dynamic_blocks_per_sm(int* out) {
     return CK_B200_OK;
 }
 
-// Opt the shared-memory variant in to 72 KB per block, once per device and dtype.
-template <int DT>
-int dynamic_smem_ready() {
+// Opt the on-chip kernels in to 72 KB per block, once per device, dtype and form.
+template <int DT, bool DYNAMIC>
+int onchip_ready() {
     static std::mutex mu;
     static int cache[64] = {0};
     int dev = 0;
@@ -577,14 +625,42 @@ int dynamic_smem_ready() {
     if (dev < 0 || dev >= 64) return fail(CK_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
     std::lock_guard<std::mutex> lock(mu);
     if (cache[dev] == 0) {
-        constexpr int kBytes = kWarpsPerBlock * kDynamicSmemMaxUnits * 512;
-        CKB_CUDA_OK(cudaFuncSetAttribute(quantize_nvfp4_dynamic_smem_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
+        constexpr int kBytes = kWarpsPerBlock * kOnchipMaxUnits * 512;
+        CKB_CUDA_OK(cudaFuncSetAttribute(quantize_nvfp4_onchip_kernel<DT, DYNAMIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes));
         int n = 0;
-        CKB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_nvfp4_dynamic_smem_kernel<DT>,
+        CKB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_nvfp4_onchip_kernel<DT, DYNAMIC>,
                                                                   kWarpsPerBlock * 32, kBytes));
         cache[dev] = n >= kBlocksPerSM ? 1 : -1;
     }
     return cache[dev] > 0 ? CK_B200_OK : -1;   // -1: not an error, the caller takes the other variant
+}
+
+template <int DT>
+int launch_quantize_onchip(const QuantArgs& a_in, int sms, cudaStream_t stream, bool* launched) {
+    *launched = false;
+    if constexpr (DT != CK_B200_DTYPE_F32) {
+        QuantArgs a = a_in;
+        const long long total = (long long)a.row_groups * a.sf_cbg;
+        const long long resident_warps = (long long)kBlocksPerSM * sms * kWarpsPerBlock;
+        int per_warp = (int)round_up64(ceil_div64(total, resident_warps), 2);
+        if (per_warp < 2) per_warp = 2;
+        if (per_warp > kOnchipMaxUnits || a.sf_cbg % 2 != 0 || a.rows % 128 != 0 || a.cols % 128 != 0 || a.rows != a.prow ||
+            a.cols != a.pcol)
+            return CK_B200_OK;
+        const int ready = onchip_ready<DT, false>();
+        if (ready > 0) return ready;
+        if (ready != CK_B200_OK) return CK_B200_OK;   // does not fit three to an SM on this device: the other kernels
+        const unsigned blocks = (unsigned)ceil_div64(ceil_div64(total, per_warp), kWarpsPerBlock);
+        a.seg_units = a.sf_cbg;
+        a.segments = 1;
+        const cudaError_t err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_onchip_kernel<DT, false>, dim3(blocks),
+                                                 dim3(32, kWarpsPerBlock), (size_t)kWarpsPerBlock * per_warp * 512, stream, a,
+                                                 (float*)nullptr, (DynamicSync*)nullptr, per_warp, total, 0u, 0ll);
+        g_launches.fetch_add(1);
+        CKB_CUDA_OK(err);
+        *launched = true;
+    }
+    return CK_B200_OK;
 }
 
 template <int DT>
@@ -606,12 +682,12 @@ int launch_quantize_dynamic(QuantArgs a, float* scale_out, void* sync, int sms, 
     bool launched = false;
     if constexpr (DT != CK_B200_DTYPE_F32) {
         // small enough to stay on chip between the phases, and no padding anywhere
-        if (g_dynamic_smem.load() && per_sm == kBlocksPerSM && per_warp <= kDynamicSmemMaxUnits && a.rows % 128 == 0 &&
+        if (g_dynamic_smem.load() && per_sm == kBlocksPerSM && per_warp <= kOnchipMaxUnits && a.rows % 128 == 0 &&
             a.cols % 128 == 0 && a.rows == a.prow && a.cols == a.pcol) {
-            const int ready = dynamic_smem_ready<DT>();
+            const int ready = onchip_ready<DT, true>();
             if (ready > 0) return ready;
             if (ready == CK_B200_OK) {
-                err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_dynamic_smem_kernel<DT>, dim3(blocks),
+                err = launch_dependent(kLaunchFamilyQuantize, quantize_nvfp4_onchip_kernel<DT, true>, dim3(blocks),
                                        dim3(32, kWarpsPerBlock), (size_t)kWarpsPerBlock * per_warp * 512, stream, a, scale_out,
                                        (DynamicSync*)sync, per_warp, total, expected, wait_cycles);
                 launched = true;

@@ -275,6 +275,9 @@ int ck_b200_read_gemm_counters(long long* out5);
 #define CK_B200_TUNE_GEMM_MAX_PAIRS 9 /* n > 0: the CTA-pair GEMM (and its all-gather form) launches at most n pairs of CTAs
                                        instead of one per pair of SMs, so that two such kernels on two streams run side by
                                        side; 0 (default) = all */
+#define CK_B200_TUNE_QUANT_ONCHIP 10 /* non-zero (default): quantize_nvfp4 of a 16-bit input of up to about 32 MB with rows and
+                                       columns multiples of 128 asks for the whole input at once (asynchronous copies into
+                                       shared memory) instead of walking it with a register ring */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus
