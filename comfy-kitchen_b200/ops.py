@@ -515,4 +515,12 @@ def read_device_status() -> int:
     rc = _lib.load().ck_b200_read_device_status(ctypes.byref(v))
     if rc not in (0, 4):      # 4 = CK_B200_ERR_DEVICE_STATUS: the word itself says which wait ran out
         _lib.check(rc, "read_device_status")
+    if v.value != 0:
+        # a kernel that gave up on a wait may have left its counters (the dynamic quantizer's meeting point, the
+        # in-GEMM quantizer's progress words) part-way: the device is idle now (the call above synchronised), so
+        # put them back to zero for the calls that follow
+        for t in _DYN_SYNC.values():
+            t.zero_()
+        for ws in _LINEAR_WS.values():
+            ws[: 1 << 16].zero_()
     return int(v.value)

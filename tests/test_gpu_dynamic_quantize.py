@@ -123,3 +123,22 @@ def test_meeting_point_wait_runs_out_and_reports(ckb):
     ts2 = ckb.dynamic_scale_nvfp4(x)
     q2, sf2 = ckb.quantize_nvfp4(x, ts2)
     assert torch.equal(ts, ts2) and torch.equal(q, q2) and ckb.read_device_status() == 0
+
+
+def test_default_counters_recover_after_an_expired_wait(ckb):
+    """The same expiry on the counters the Python operator keeps per stream: reading the status word puts them back to
+    zero, so the calls that follow on that stream work (without that, every later launch would wait out its limit)."""
+    x = seeded_randn((16, 256), seed=2).cuda()
+    ckb.quantize_nvfp4_dynamic(x)                        # creates this stream's counters
+    prev = ckb.set_tuning(6, 1)
+    try:
+        ckb.quantize_nvfp4_dynamic(x)
+        status = ckb.read_device_status()
+    finally:
+        ckb.set_tuning(6, prev)
+    assert status == 8
+    q, sf, ts = ckb.quantize_nvfp4_dynamic(x)
+    ts2 = ckb.dynamic_scale_nvfp4(x)
+    q2, sf2 = ckb.quantize_nvfp4(x, ts2)
+    assert torch.equal(ts, ts2) and torch.equal(q, q2) and torch.equal(sf.view(torch.uint8), sf2.view(torch.uint8))
+    assert ckb.read_device_status() == 0
