@@ -13,11 +13,11 @@ from .backend import install, uninstall
 from .build import build_library
 from .ops import (dequantize_mxfp8, dequantize_nvfp4, dynamic_scale_nvfp4, launches, linear_nvfp4, quantize_mxfp8,
                   quantize_nvfp4, quantize_nvfp4_dynamic, read_device_status, read_gemm_counters, scaled_mm_mxfp8,
-                  scaled_mm_nvfp4, set_tuning)
+                  scaled_mm_nvfp4, set_tuning, promise_resident_weights)
 from .linear import NVFP4Linear
 from .sharded import PeerGroup, PeerMemory, ShardedNVFP4Linear, shard_rows
 
 __all__ = [
     "quantize_nvfp4", "quantize_nvfp4_dynamic", "dequantize_nvfp4", "scaled_mm_nvfp4", "dynamic_scale_nvfp4", "linear_nvfp4", "quantize_mxfp8", "dequantize_mxfp8", "scaled_mm_mxfp8", "install", "uninstall",
-    "build_library", "NVFP4Linear", "PeerGroup", "PeerMemory", "ShardedNVFP4Linear", "shard_rows", "set_tuning", "launches", "read_device_status", "read_gemm_counters",
+    "build_library", "NVFP4Linear", "PeerGroup", "PeerMemory", "ShardedNVFP4Linear", "shard_rows", "set_tuning", "promise_resident_weights", "launches", "read_device_status", "read_gemm_counters",
 ]

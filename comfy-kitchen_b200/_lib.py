@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
 
 QUERY_ABI_VERSION, QUERY_SM_COUNT, QUERY_WORKSPACE_BYTES, QUERY_COMPUTE_CAPABILITY, QUERY_LAUNCHES, QUERY_LAST_GEMM_SPLITS = range(6)
 TUNE_QUANT_VARIANT, TUNE_GEMM_VARIANT = 0, 1
+TUNE_GEMM_SKINNY, TUNE_WEIGHTS_RESIDENT = 11, 12
 
 _lib = None
 

@@ -59,10 +59,13 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         if verbose:
             print(r.stderr)
         objs.append(obj)
-    cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs]
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = os.path.join(build_dir, "libck_b200.so.new")
+    cmd = [_nvcc(), "-shared", "-o", tmp, *objs]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env)
     if r.returncode != 0:
         raise RuntimeError(f"linking libck_b200.so failed:\n{r.stderr}")
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -83,6 +83,9 @@ struct GemmArgs {
                           // rows that are never stored)
     int tma_store;        // non-zero: 16-bit output written through shared memory and TMA stores
     int debug;            // non-zero: CTA 0 prints the cycles its roles spent waiting
+    int early_weights;    // one-CTA kernel: non-zero = B and its scales of the first ring of stages are requested before
+                          // the wait for the preceding kernel of the stream (the caller's promise: nothing in flight
+                          // writes them)
     // fused all-gather (CTA-pair kernel, 16-bit output): `out` is this rank's column block inside its own
     // [M, ld_out] matrix and every staged tile is also stored to the same block of the other ranks' matrices
     int64_t ld_out;       // row stride of the output matrix in elements (N for a plain GEMM)
@@ -90,18 +93,30 @@ struct GemmArgs {
     uint8_t* peer_out[7]; // origin of the column block in each peer's matrix, as mapped into this process
 };
 
-template <int BN>
+// AROWS < 128 (with BN = 64: the configuration for one short tile row, M <= 64): A's share of a stage shrinks to the rows
+// that exist, tiles are 64 columns wide and two CTAs fit on an SM, so that N / 64 (times the K splits) CTAs of short
+// rings have the weight's bytes in flight on every SM at once.  The MMA still reads 128 rows of A; the rows past AROWS
+// are whatever follows in shared memory and feed accumulator rows that are never stored.
+template <int BN, int AROWS = BM>
 struct Cfg {
-    static constexpr int kStages = (BN == 128) ? 6 : 4;
-    static constexpr int kBands = BN / 128;                       // 128-row bands of B per tile
-    static constexpr int kABytes = BM * BK_BYTES;                 // 16 KiB
+    static constexpr bool kSkinny = BN < 128;
+    static constexpr int kCtasPerSm = kSkinny ? 2 : 1;
+    static constexpr int kBands = kSkinny ? 1 : BN / 128;         // 128-row bands of B scales per tile
+    static constexpr int kABytes = AROWS * BK_BYTES;              // 16 KiB for full tiles
     static constexpr int kBBytes = BN * BK_BYTES;
     static constexpr int kSfaBytes = CHUNKS * SF_CHUNK_BYTES;     // 2 KiB
     static constexpr int kSfbBytes = kBands * CHUNKS * SF_CHUNK_BYTES;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
     static constexpr int kStagingBytes = 4 * STAGING_BYTES_PER_WARP;   // 8 KiB, one tile per epilogue warp
     static constexpr int kBarrierBytes = 256;
+    // two CTAs per SM: (228 KiB - 1 KiB reserved per CTA) / 2
+    static constexpr int kSmemBudget = kSkinny ? 115712 : 232448;
+    // as many stages as fit: 6 (128 x 128) or 4 (128 x 256) with full A tiles; 6 / 5 for 64-column tiles with 32 / 64 A rows
+    static constexpr int kStages = (kSmemBudget - kStagingBytes - 1024 - kBarrierBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + kBarrierBytes;
+    static_assert(!kSkinny || (kStageBytes >= BM * BK_BYTES && kABytes % 1024 == 0),
+                  "the MMA's 128 A rows stay inside the stage; B stays 1024-byte aligned");
+    static_assert(kStages >= 3 && 2 * kStages + 5 <= 30, "ring depth and barrier room");
     // tensor-memory columns: two accumulators (overlapping by kOverlapCols when BN = 256), then two alternating
     // scale-factor regions, each holding the scales of two 64-element steps
     static constexpr int kOverlapCols = (BN == 256) ? 64 : 0;
@@ -110,9 +125,9 @@ struct Cfg {
     static constexpr int kSfaColsHalf = 2 * 4;
     static constexpr int kSfbColsHalf = 2 * 4 * kBands;
     static constexpr int kSfRegionCols = kSfaColsHalf + kSfbColsHalf;
-    static constexpr int kTmemCols = 512;
+    static constexpr int kTmemCols = kSkinny ? 256 : 512;         // per CTA; kCtasPerSm of them share the SM's 512
     static_assert(kSfCol0 + 2 * kSfRegionCols <= kTmemCols, "tensor memory budget");
-    static_assert(kSmemBytes <= 232448, "shared memory budget");
+    static_assert(kSmemBytes <= kSmemBudget, "shared memory budget");
     // instruction descriptor of tcgen05.mma.kind::mxf4nvf4.block_scale: A,B = packed e2m1 (format 1), K-major,
     // UE4M3 scales, N >> 3 at bit 17, M >> 4 at bit 24
     static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (0u << 23) |
@@ -322,11 +337,12 @@ __device__ __forceinline__ void tile_coords(const GemmArgs& g, int tile, int& tm
 // FMT 0: NVFP4 (packed e2m1, e4m3 scales per 16 elements, 256 elements of K per stage).
 // FMT 1: MXFP8 (e4m3 bytes, e8m0 scales per 32 elements, 128 elements of K per stage): the same 128-byte operand rows
 // and 32-byte steps per instruction, but one scale chunk per stage, whose four bytes per row serve the four instructions.
-template <int BN, bool DBG, int FMT = 0>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int BN, bool DBG, int FMT = 0, int AROWS = BM>
+__global__ void __launch_bounds__(NUM_THREADS, (Cfg<BN, AROWS>::kCtasPerSm))
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_out, const GemmArgs g) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, AROWS>;
+    static_assert(!C::kSkinny || FMT == 0, "64-column tiles: NVFP4 only");
     constexpr bool MX = (FMT == 1);
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -369,7 +385,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int total_items = g.m_tiles * g.n_tiles * g.splits;
-    grid_dependency_wait();   // barriers and tensor memory are set up while the previous kernel drains
+    // Barriers and tensor memory are set up while the previous kernel drains.  With early_weights the roles that
+    // read or write what a preceding kernel may touch (activations, their scales, the tensor scales, bias, output,
+    // partial sums) wait by themselves, and the producer asks for the weight's first stages before it does.
+    const bool early = g.early_weights != 0;
+    if (!early) grid_dependency_wait();
 
     // cycle counters of the debug build (DBG): compiled out otherwise
     auto now = [] { return DBG ? clock64() : 0ll; };
@@ -379,40 +399,73 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+        bool waited_for_grid = !early;
         long long waited = 0;
         const long long t_begin = now();
+        if (early && (int)blockIdx.x >= total_items) grid_dependency_wait();
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             const int tile = item / g.splits;
             const int kb0 = (item - tile * g.splits) * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);
             int tm, tn;
             tile_coords(g, tile, tm, tn);
+            // first 128-row band of B scales of this tile (a 64-column tile uses half of one band's chunks)
+            const int band0 = C::kSkinny ? (tn * BN) / 128 : tn * C::kBands;
             int sfb_present = 0;
 #pragma unroll
             for (int b = 0; b < C::kBands; ++b)
-                if (tn * C::kBands + b < g.sfb_bands) ++sfb_present;
+                if (band0 + b < g.sfb_bands) ++sfb_present;
             const uint8_t* sfa_src = g.sfa + (int64_t)tm * g.sf_cbg * SF_CHUNK_BYTES;
-            const uint8_t* sfb_src = g.sfb + (int64_t)tn * C::kBands * g.sf_cbg * SF_CHUNK_BYTES;
-            for (int kb = kb0; kb < kb1; ++kb) {
+            const uint8_t* sfb_src = g.sfb + (int64_t)band0 * g.sf_cbg * SF_CHUNK_BYTES;
+            __syncwarp();
+            // one stage's loads in two parts: what belongs to the weight, and what a preceding kernel may have written
+            auto load_weight_part = [&](int kb, int stg) {
+                const uint32_t st = smem_u32(smem) + stg * C::kStageBytes;
+                const uint32_t bar = smem_u32(&full_bar[0]) + stg * 8;
+                const int chunk0 = MX ? kb : kb * CHUNKS;   // first scale chunk of this stage
+                const int nchunk = MX ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                const uint32_t sf_bytes = nchunk * SF_CHUNK_BYTES;
+                mbar_expect_tx(bar, g.a_box_bytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
+                tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * BN, bar);
+#pragma unroll
+                for (int b = 0; b < C::kBands; ++b)
+                    if (b < sfb_present)
+                        bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes,
+                                  sfb_src + ((int64_t)b * g.sf_cbg + chunk0) * SF_CHUNK_BYTES, sf_bytes, bar);
+            };
+            auto load_activation_part = [&](int kb, int stg) {
+                const uint32_t st = smem_u32(smem) + stg * C::kStageBytes;
+                const uint32_t bar = smem_u32(&full_bar[0]) + stg * 8;
+                const int chunk0 = MX ? kb : kb * CHUNKS;
+                const int nchunk = MX ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+                tma_load_2d(st, &tmap_a, kb * BK_BYTES, tm * BM, bar);
+                bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)chunk0 * SF_CHUNK_BYTES, nchunk * SF_CHUNK_BYTES, bar);
+            };
+            int kb = kb0;
+            if (!waited_for_grid) {
+                // the CTA's first work item: every stage of the ring is free.  Weight parts of as many stages as the
+                // ring holds, then the wait for the preceding kernel, then the activation parts.
+                const int n_pre = min(C::kStages, kb1 - kb0);
+                if (elect_one())
+                    for (int i = 0; i < n_pre; ++i) load_weight_part(kb0 + i, i);
+                __syncwarp();
+                grid_dependency_wait();
+                waited_for_grid = true;
+                if (elect_one())
+                    for (int i = 0; i < n_pre; ++i) load_activation_part(kb0 + i, i);
+                __syncwarp();
+                kb = kb0 + n_pre;
+                stage = n_pre;
+                if (stage == C::kStages) { stage = 0; phase ^= 1; }
+            }
+            for (; kb < kb1; ++kb) {
                 const long long t0 = now();
                 ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
                 waited += now() - t0;
                 if (!ok) break;
-                const uint32_t st = smem_u32(smem) + stage * C::kStageBytes;
-                const uint32_t bar = smem_u32(&full_bar[0]) + stage * 8;
-                const int chunk0 = MX ? kb : kb * CHUNKS;   // first scale chunk of this stage
-                const int nchunk = MX ? 1 : min(CHUNKS, g.sf_cbg - kb * CHUNKS);
-                const uint32_t sf_bytes = nchunk * SF_CHUNK_BYTES;
                 if (elect_one()) {
-                    mbar_expect_tx(bar, g.a_box_bytes + C::kBBytes + (1 + sfb_present) * sf_bytes);
-                    tma_load_2d(st, &tmap_a, kb * BK_BYTES, tm * BM, bar);
-                    tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * BN, bar);
-                    bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)chunk0 * SF_CHUNK_BYTES, sf_bytes, bar);
-#pragma unroll
-                    for (int b = 0; b < C::kBands; ++b)
-                        if (b < sfb_present)
-                            bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + b * C::kSfaBytes,
-                                      sfb_src + ((int64_t)b * g.sf_cbg + chunk0) * SF_CHUNK_BYTES, sf_bytes, bar);
+                    load_weight_part(kb, stage);
+                    load_activation_part(kb, stage);
                 }
                 __syncwarp();
                 if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -432,6 +485,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t sf_t0 = tmem_base + C::kSfCol0;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local_tile) {
             const int kb0 = (item % g.splits) * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);
+            // a 64-column tile's scales are two of the four tensor-memory columns its band's chunk fills (32 rows of the
+            // band per column): the instruction reads from the column its first row sits in
+            uint32_t sfb_col = 0;
+            if (C::kSkinny) {
+                int tm, tn;
+                tile_coords(g, item / g.splits, tm, tn);
+                sfb_col = (uint32_t)(((tn * BN) % 128) / 32);
+            }
             long long t0 = now();
             // the accumulator's own columns: drained by the epilogue two tiles ago
             ok = mbar_wait(smem_u32(&acc_empty_bar[acc]), acc_phase ^ 1, abort_flag, WAIT_ACC_EMPTY);
@@ -497,7 +558,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                 sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
                             // 64 elements of K = 32 bytes = 2 descriptor address units inside the swizzle row
                             tc_mma(d_tmem, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
-                                   C::kIdesc, sfa_t, sfb_t, (j != 0 || kb != kb0) ? 1u : 0u);
+                                   C::kIdesc, sfa_t, sfb_t + sfb_col, (j != 0 || kb != kb0) ? 1u : 0u);
                         }
                     }
                     tc_commit(smem_u32(&empty_bar[0]) + stage * 8);   // stage reusable once these MMAs have read it
@@ -522,6 +583,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         bool ok = true;
         long long wait_acc = 0;
         const long long t_begin = now();
+        if (early) grid_dependency_wait();   // before the tensor scales are read and anything is stored
         const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
         uint8_t* my_staging = staging + quad * STAGING_BYTES_PER_WARP;
         const uint32_t my_staging_u32 = smem_u32(my_staging);
@@ -1511,10 +1573,12 @@ struct SplitScratch {
     size_t partial_bytes = 0;
 };
 
-template <int BN, int FMT = 0>
+template <int BN, int FMT = 0, int AROWS = BM>
 int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cudaStream_t stream, SplitScratch scratch) {
-    using C = Cfg<BN>;
-    auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true, FMT> : gemm_nvfp4_kernel<BN, false, FMT>;
+    using C = Cfg<BN, AROWS>;
+    auto kernel = g.debug ? gemm_nvfp4_kernel<BN, true, FMT, AROWS> : gemm_nvfp4_kernel<BN, false, FMT, AROWS>;
+    if (AROWS < BM && g.M > AROWS) return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm: %d rows do not fit this tile configuration", g.M);
+    const int capacity = sms * C::kCtasPerSm;   // CTAs resident at once
     const int64_t row_bytes = FMT == 1 ? K : K / 2;   // e4m3 bytes or packed e2m1 nibbles
     // opting in to large dynamic shared memory is per function and per device: once
     {
@@ -1528,11 +1592,14 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
             if (attr_err != cudaSuccess)
                 return fail(CK_B200_ERR_CUDA, "cudaFuncSetAttribute(shared memory %d) failed: %s", C::kSmemBytes,
                             cudaGetErrorString(attr_err));
+            // all of the SM's configurable memory as shared memory, so that kCtasPerSm CTAs fit
+            if (C::kCtasPerSm > 1)
+                CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
             if (dev >= 0 && dev < 64) done[g.debug ? 1 : 0][dev] = true;
         }
     }
     CUtensorMap ma, mb, mo;
-    const int a_box_rows = g.M <= 32 ? 32 : g.M <= 64 ? 64 : BM;
+    const int a_box_rows = g.M <= 32 ? 32 : g.M <= 64 ? 64 : BM;   // never more than AROWS (checked above)
     g.a_box_bytes = a_box_rows * BK_BYTES;
     if (int rc = make_operand_map(&ma, a, g.M, row_bytes, a_box_rows)) return rc;
     if (int rc = cached_operand_map(&mb, b, g.N, row_bytes, BN)) return rc;   // the weight: the same matrix call after call
@@ -1546,8 +1613,9 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     g.splits = 1;
     g.k_per_split = g.k_iters;
     g.partial = nullptr;
+    g.early_weights = (g.m_tiles == 1 && g_weights_resident.load() != 0) ? 1 : 0;
     if (g.m_tiles == 1 && scratch.partial != nullptr) {
-        g.splits = choose_splits(g.n_tiles, g.k_iters, sms, g.M, g.N, scratch.partial_bytes);
+        g.splits = choose_splits(g.n_tiles, g.k_iters, capacity, g.M, g.N, scratch.partial_bytes);
         if (g.splits > 1) {
             g.k_per_split = (int)ceil_div64(g.k_iters, g.splits);
             g.splits = (int)ceil_div64(g.k_iters, g.k_per_split);   // no empty work items
@@ -1563,7 +1631,7 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     }
     g_last_splits.store(g.splits);
     const int64_t items = (int64_t)g.m_tiles * g.n_tiles * g.splits;
-    const unsigned grid = (unsigned)(items < sms ? items : sms);
+    const unsigned grid = (unsigned)(items < capacity ? items : capacity);
     const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3(grid), dim3(NUM_THREADS), C::kSmemBytes, stream, ma, mb, mo, g);
     g_launches.fetch_add(1);
     CKB_CUDA_OK(err);
@@ -1643,10 +1711,15 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     g.n_peers = 0;
     for (int p = 0; p < 7; ++p) g.peer_out[p] = nullptr;
     g.debug = g_gemm_debug.load();
+    g.early_weights = 0;
     int variant = g_gemm_variant.load();
     // CTA pairs with 256x256 tiles when the problem has more than one tile row and column; otherwise one CTA per
     // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
-    if (variant == 0) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
+    // variant 5 = the short-row configuration where it applies (M <= 64), the automatic choice elsewhere
+    // (automatic: from 64 such tiles up - measured on M = 16: 128 <= N <= 2560 at K = 4096 is 3-4 % faster on 128-column
+    // tiles with their split-K, N >= 4096 equal or faster on 64-column tiles)
+    const bool skinny = M <= 64 && (variant == 5 || (variant == 0 && g_gemm_skinny.load() != 0 && N >= 4096));
+    if (variant == 0 || variant == 5) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
     if ((uintptr_t)scratch.partial & 15)
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
@@ -1671,6 +1744,9 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     if (variant == 4 && M > 128) return launch_gemm_pair<64>(a_dev, b_dev, g, K, s);
     if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch);
+    // one short tile row: 64-column tiles, two CTAs per SM (every SM streams its share of the weight from the start)
+    if (skinny && M <= 32) return launch_gemm<64, 0, 32>(a_dev, b_dev, g, K, sms, s, scratch);
+    if (skinny && M <= 64) return launch_gemm<64, 0, 64>(a_dev, b_dev, g, K, sms, s, scratch);
     // one tile row: 128-column tiles give the most work items, and split-K (with scratch) fills the remaining SMs
     return launch_gemm<128>(a_dev, b_dev, g, K, sms, s, scratch);
 }

@@ -494,6 +494,16 @@ def set_tuning(key: int, value: int) -> int:
     return int(_lib.load().ck_b200_set_tuning(key, value))
 
 
+def promise_resident_weights(resident: bool = True) -> bool:
+    """The caller's promise that, whenever a GEMM with M <= 128 is enqueued, nothing still in flight on the GPU writes
+    its weight operand or weight scales (weights quantized when the model was loaded and synchronised since).  The GEMM
+    then asks for the first stages of its weight before it waits for the preceding kernel of the stream, so a stack of
+    small-M layers streams the next layer's weight under the current layer's tail.  Everything a preceding kernel may
+    have produced (activations, their scales, tensor scales, bias) and every store still waits.  Returns the previous
+    setting; off by default."""
+    return bool(set_tuning(_lib.TUNE_WEIGHTS_RESIDENT, 1 if resident else 0))
+
+
 def launches() -> int:
     """Kernels this library has launched in this process."""
     return int(_lib.load().ck_b200_query(_lib.QUERY_LAUNCHES))

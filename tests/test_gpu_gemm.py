@@ -22,7 +22,7 @@ def ckb():
     return m
 
 
-@pytest.fixture(params=[1, 2, 3, 4], ids=["bn128", "bn256", "pair256", "pair256-k128"])
+@pytest.fixture(params=[1, 2, 3, 4, 5], ids=["bn128", "bn256", "pair256", "pair256-k128", "short-rows-bn64"])
 def variant(request, ckb):
     prev = ckb.set_tuning(1, request.param)
     yield request.param
@@ -193,6 +193,92 @@ def test_split_k_repeats_and_graph_replays(mnk, ckb):
         graph.replay()
     stream.synchronize()
     assert torch.equal(y, want)
+    assert ckb.read_device_status() == 0
+
+
+SHORT_ROWS = [(16, 10240, 4096), (64, 10240, 4096), (1, 12288, 1024), (33, 10248, 4096), (16, 4096, 10240),
+              (64, 4096, 10240), (48, 72, 96), (8, 8, 32)]
+
+
+@pytest.mark.parametrize("mnk", SHORT_ROWS, ids=lambda s: "x".join(map(str, s)))
+def test_short_row_tiles_match_128_column_tiles(mnk, ckb):
+    """M <= 64 on 64-column tiles with two CTAs per SM (a tile reads its scales from half of a 128-row band's chunk
+    in tensor memory): bit-identical to the 128-column tiles whenever both cut K into the same number of splits,
+    within the GEMM tolerance otherwise; N tails and single-tile problems included."""
+    from comfy_kitchen_b200 import _lib
+    M, N, K = mnk
+    x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=3 * M + N + K)
+    bias = seeded_randn((1, N), seed=5, std=0.5).reshape(N).cuda()
+    prev = ckb.set_tuning(1, 1)
+    try:
+        ref = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
+        splits_ref = _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
+        ckb.set_tuning(1, 5)
+        for _ in range(3):
+            y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
+            splits = _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
+            if splits == splits_ref:
+                assert torch.equal(y, ref)
+            else:
+                assert rel_rms(y[:M].float(), ref[:M].float()) <= 1e-3
+    finally:
+        ckb.set_tuning(1, prev)
+    assert ckb.read_device_status() == 0
+
+
+@pytest.mark.parametrize("mnk", [(16, 10240, 4096), (64, 4096, 10240), (128, 4096, 4096), (1, 4096, 4096)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_weight_loads_ahead_of_the_preceding_kernel(mnk, ckb):
+    """With the caller's promise that weights are resident, a small-M GEMM asks for its weight before it waits for the
+    preceding kernel of the stream.  Activations, their scales and the tensor scale are produced by the kernels right
+    before it on the same stream with no synchronisation in between, so the test fails if anything but the weight is
+    read early: a stack of layers captured in one graph, replayed on changed activations, must give the bits of the
+    same stack without the promise."""
+    M, N, K = mnk
+    layers = []
+    for i in range(4):
+        w = seeded_randn((N, K), seed=100 + i, std=0.02).cuda()
+        tsw = amax_scale(w).cuda()
+        qw, sfw = ckb.quantize_nvfp4(w, tsw)
+        layers.append((qw, sfw, tsw, seeded_randn((1, N), seed=7 + i, std=0.5).reshape(N).cuda()))
+    xs = [seeded_randn((M, K), seed=50 + j).cuda() for j in range(3)]
+    x = xs[0].clone()
+
+    def stack():
+        outs = []
+        for qw, sfw, tsw, bias in layers:
+            qx, sfx, tsx = ckb.quantize_nvfp4_dynamic(x, pad_16x=M % 16 != 0)   # written by the kernel right before the GEMM
+            outs.append(ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias))
+        return outs
+
+    torch.cuda.synchronize()      # the promise: the weights above are complete and stay untouched
+    want = []
+    for xj in xs:
+        x.copy_(xj)
+        want.append([o.clone() for o in stack()])
+    prev = ckb.promise_resident_weights(True)
+    try:
+        for j, xj in enumerate(xs):
+            x.copy_(xj)
+            for o, wnt in zip(stack(), want[j]):
+                assert torch.equal(o, wnt)
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            stack()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream), torch.cuda.graph(graph):
+            outs = stack()
+        for rep in range(6):
+            j = rep % 3
+            with torch.cuda.stream(stream):
+                x.copy_(xs[j], non_blocking=True)     # the activations change right before the replay, on its stream
+                graph.replay()
+            stream.synchronize()
+            for o, wnt in zip(outs, want[j]):
+                assert torch.equal(o, wnt)
+    finally:
+        ckb.promise_resident_weights(prev)
     assert ckb.read_device_status() == 0
 
 
