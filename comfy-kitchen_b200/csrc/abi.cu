@@ -15,6 +15,7 @@ std::atomic<int> g_last_splits{1};
 std::atomic<int> g_gemm_max_pairs{0};
 std::atomic<int> g_gemm_skinny{1};
 std::atomic<int> g_weights_resident{0};
+std::atomic<int> g_gemm_cluster_split{0};
 std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
@@ -109,6 +110,7 @@ int ck_b200_set_tuning(int key, int value) {
         case CK_B200_TUNE_DYNAMIC_SMEM: return ckb::g_dynamic_smem.exchange(value);
         case CK_B200_TUNE_GEMM_MAX_PAIRS: return ckb::g_gemm_max_pairs.exchange(value);
         case CK_B200_TUNE_QUANT_ONCHIP: return ckb::g_quant_onchip.exchange(value);
+        case CK_B200_TUNE_GEMM_CLUSTER_SPLITK: return ckb::g_gemm_cluster_split.exchange(value);
         case CK_B200_TUNE_WEIGHTS_RESIDENT: return ckb::g_weights_resident.exchange(value);
         case CK_B200_TUNE_GEMM_SKINNY: return ckb::g_gemm_skinny.exchange(value);
         default: return -1;

@@ -26,6 +26,7 @@ extern std::atomic<int> g_gemm_debug;
 extern std::atomic<int> g_dependent_launch;
 extern std::atomic<int> g_gemm_max_pairs;   // > 0: the CTA-pair GEMM launches at most this many pairs (CK_B200_TUNE_GEMM_MAX_PAIRS)
 extern std::atomic<int> g_gemm_skinny;      // non-zero: M <= 64 takes the 64-column, two-CTAs-per-SM configuration (CK_B200_TUNE_GEMM_SKINNY)
+extern std::atomic<int> g_gemm_cluster_split;   // non-zero: M <= 64 splits K over a thread-block cluster (CK_B200_TUNE_GEMM_CLUSTER_SPLITK)
 extern std::atomic<int> g_weights_resident;   // the caller's promise behind GemmArgs::early_weights (CK_B200_TUNE_WEIGHTS_RESIDENT)
 extern std::atomic<int> g_last_splits;   // K-splits of the most recent GEMM launch (CK_B200_QUERY_LAST_GEMM_SPLITS)
 

@@ -177,6 +177,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// Brings a tensor map (a kernel parameter) into the cache the TMA unit reads it from, ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
                  "r"(y), "r"(src)
@@ -360,6 +364,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     allow_dependent_launch();
+    if (threadIdx.x == 32) {   // the maps are parameters: nothing a preceding kernel writes
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+        if (g.tma_store) prefetch_tensormap(&tmap_out);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -471,7 +480,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (++stage == C::kStages) { stage = 0; phase ^= 1; }
             }
         }
-        if (DBG && g.debug == 1 && blockIdx.x == 0 && lane == 0)
+        if (DBG && (g.debug & 1) && blockIdx.x == 0 && lane == 0)
             printf("[gemm bn%d cta0] producer: total %lld cycles, waiting for free stages %lld\n", BN, now() - t_begin,
                    waited);
     } else if (warp == 1) {
@@ -539,7 +548,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     // overwrites scales that the MMAs issued just before it still read)
 #pragma unroll
                     for (int j = 0; j < CHUNKS; ++j) {
-                        if (j < nchunk) {
+                        if (j < nchunk && !(DBG && (g.debug & 4))) {   // experiment: timing without the scale copies
                             const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
                             const uint32_t sfb_t =
                                 sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
@@ -572,7 +581,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
-        if (DBG && g.debug == 1 && blockIdx.x == 0 && lane == 0)
+        if (DBG && (g.debug & 1) && blockIdx.x == 0 && lane == 0)
             printf("[gemm bn%d cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", BN,
                    now() - t_begin, wait_acc, wait_full);
     } else {
@@ -675,7 +684,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (acc == 0) acc_phase ^= 1;
         }
         if (g.tma_store && lane == 0) tma_store_wait_all();   // global writes complete before the CTA exits
-        if (DBG && g.debug == 1 && blockIdx.x == 0 && threadIdx.x == 64)
+        if (DBG && (g.debug & 1) && blockIdx.x == 0 && threadIdx.x == 64)
             printf("[gemm bn%d cta0] epilogue: total %lld cycles, waiting for accumulators %lld\n", BN, now() - t_begin,
                    wait_acc);
     }
@@ -857,6 +866,13 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     allow_dependent_launch();
+    if (threadIdx.x == 32) {   // the maps are parameters: nothing a preceding kernel writes
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+        prefetch_tensormap(&tmap_sfa);
+        prefetch_tensormap(&tmap_sfb);
+        if (g.tma_store) prefetch_tensormap(&tmap_out);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) {
@@ -974,7 +990,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 if (++stage == kStages2) { stage = 0; phase ^= 1; }
             }
         }
-        if (DBG && g.debug == 1 && pair == 0 && lane == 0)
+        if (DBG && (g.debug & 1) && pair == 0 && lane == 0)
             printf("[gemm pair cta%u] producer: total %lld cycles, waiting for free stages %lld, for quantized bands %lld\n",
                    rank, now() - t_begin, waited, q_waited);
     } else if (warp == 1 && rank == 0) {
@@ -1032,7 +1048,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 } else if (elect_one()) {
 #pragma unroll
                     for (int j = 0; j < kChunks; ++j) {
-                        if (j < nchunk) {
+                        if (j < nchunk && !(DBG && (g.debug & 4))) {   // experiment: timing without the scale copies
                             const uint32_t sf_r = sf_t0 + (region0 + (j >> 1)) * kSfRegion2;
                             const uint32_t sfa_t = sf_r + (j & 1) * 4;
                             const uint32_t sfb_t = sf_r + 8 + (j & 1) * 8;
@@ -1068,7 +1084,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         if (DBG && pair == 0 && lane == 0) {
             const long long cyc = now() - t_begin;
-            if (g.debug == 1) printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", cyc,
+            if ((g.debug & 1)) printf("[gemm pair cta0] mma: total %lld cycles, waiting for accumulator %lld, for loaded stages %lld\n", cyc,
                    wait_acc, wait_full);
             g_gemm_counters[2] = wait_full;
             g_gemm_counters[3] = wait_acc;
@@ -1094,7 +1110,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     if (atomicAdd(&fq.sync->band[band], 1u) + 1u == (uint32_t)per_band) atomicAdd(&fq.sync->bands_done, 1u);
                 }
             }
-            if (DBG && g.debug == 1 && pair == 0 && threadIdx.x == NUM_THREADS)
+            if (DBG && (g.debug & 1) && pair == 0 && threadIdx.x == NUM_THREADS)
                 printf("[gemm pair cta%u] quantizer: total %lld cycles\n", rank, now() - t_begin);
         }
     } else if (warp >= 2) {
@@ -1241,7 +1257,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         else if (g.tma_store && lane == 0) tma_store_wait_all();
         if (DBG && pair == 0 && threadIdx.x == 64) {
             const long long cyc = now() - t_begin, ns = now_ns() - t_begin_ns;
-            if (g.debug == 1) printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank, cyc,
+            if ((g.debug & 1)) printf("[gemm pair cta%u] epilogue: total %lld cycles in %lld ns, waiting for accumulators %lld\n", rank, cyc,
                    ns, wait_acc);
             if (rank == 0) {
                 g_gemm_counters[0] = cyc;
@@ -1315,6 +1331,256 @@ __global__ void peer_barrier_kernel(const BarrierArgs b) {
 // ---- split-K reduction ----------------------------------------------------------------------------
 
 // out[m,n] = out_dtype( alpha * sum_s partial[s,m,n] + bias[n] ), four columns per thread (N % 8 == 0).
+// ---- one short tile row, K split over a thread-block cluster ------------------------------------------
+//
+// M <= 64: a 128-column tile of the output is computed by a cluster of CS CTAs, each over 1/CS of K (two CTAs per SM,
+// short rings), so the serial chain of stages per CTA - which is what a small-M GEMM spends its time in once the
+// weight streams at the HBM rate - is CS times shorter.  The partial sums never leave the SMs: every CTA writes the
+// 32-column steps it does not own into the owner's shared memory (distributed shared memory), one cluster barrier,
+// and every CTA adds up the steps it owns in rank order (the order of splitk_reduce_kernel, so the bits equal the
+// two-kernel split-K with the same number of splits), applies alpha and bias and stores.  One launch, no scratch.
+template <int AROWS, int CS>
+struct ClusterCfg {
+    static_assert(CS == 2 || CS == 4, "cluster size");
+    static_assert(AROWS == 32 || AROWS == 64, "A rows per stage");
+    static constexpr int kABytes = AROWS * BK_BYTES;
+    static constexpr int kBBytes = 128 * BK_BYTES;
+    static constexpr int kSfBytes = CHUNKS * SF_CHUNK_BYTES;
+    static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
+    static constexpr int kStepsOwned = 4 / CS;                            // 32-column steps a rank adds up
+    static constexpr int kSlotBytes = AROWS * kStepsOwned * EPI_COLS * 4; // what one sender leaves with an owner
+    static constexpr int kExchangeBytes = (CS - 1) * kSlotBytes;
+    static constexpr int kSmemBudget = 115712;                            // two CTAs per SM
+    static constexpr int kStages = (kSmemBudget - kExchangeBytes - 1024 - 256) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + 1024 + 256;
+    static constexpr int kSfCol0 = 128, kSfRegionCols = 16, kTmemCols = 256;
+    static_assert(kStages >= 3 && 2 * kStages + 1 <= 28, "ring depth and barrier room");
+    static_assert(kStageBytes >= BM * BK_BYTES && kStageBytes % 1024 == 0 && kABytes % 1024 == 0, "stage layout");
+};
+
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <int AROWS, int CS>
+__global__ void __cluster_dims__(CS, 1, 1) __launch_bounds__(NUM_THREADS, 2)
+gemm_nvfp4_cluster_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const GemmArgs g) {
+    using C = ClusterCfg<AROWS, CS>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* exchange = smem + C::kStages * C::kStageBytes;     // [CS - 1 senders][AROWS][kStepsOwned * 32] fp32
+    uint64_t* bars = reinterpret_cast<uint64_t*>(exchange + C::kExchangeBytes);
+    uint64_t* full_bar = bars;                                  // [kStages] producer -> MMA
+    uint64_t* empty_bar = bars + C::kStages;                    // [kStages] MMA -> producer
+    uint64_t* acc_full_bar = bars + 2 * C::kStages;             // [1] MMA -> epilogue
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int tn = blockIdx.x / CS;                             // one tile row: the tile index is the column block
+    allow_dependent_launch();
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(acc_full_bar), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    cluster_sync_all();   // every CTA of the cluster has started before any of them writes into another's shared memory
+    const bool early = g.early_weights != 0;
+    if (!early) grid_dependency_wait();
+
+    const int kb0 = (int)rank * g.k_per_split, kb1 = min(g.k_iters, kb0 + g.k_per_split);   // never empty (host)
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        const int band0 = tn;                                   // 128-column tiles: one band of B scales each
+        const bool sfb_present = band0 < g.sfb_bands;
+        const uint8_t* sfb_src = g.sfb + (int64_t)band0 * g.sf_cbg * SF_CHUNK_BYTES;
+        auto load_weight_part = [&](int kb, int stg) {
+            const uint32_t st = smem_u32(smem) + stg * C::kStageBytes;
+            const uint32_t bar = smem_u32(&full_bar[0]) + stg * 8;
+            const uint32_t sf_bytes = (uint32_t)min(CHUNKS, g.sf_cbg - kb * CHUNKS) * SF_CHUNK_BYTES;
+            mbar_expect_tx(bar, g.a_box_bytes + C::kBBytes + (sfb_present ? 2u : 1u) * sf_bytes);
+            tma_load_2d(st + C::kABytes, &tmap_b, kb * BK_BYTES, tn * 128, bar);
+            if (sfb_present)
+                bulk_load(st + C::kABytes + C::kBBytes + C::kSfBytes, sfb_src + (int64_t)kb * CHUNKS * SF_CHUNK_BYTES, sf_bytes, bar);
+        };
+        auto load_activation_part = [&](int kb, int stg) {
+            const uint32_t st = smem_u32(smem) + stg * C::kStageBytes;
+            const uint32_t bar = smem_u32(&full_bar[0]) + stg * 8;
+            const uint32_t sf_bytes = (uint32_t)min(CHUNKS, g.sf_cbg - kb * CHUNKS) * SF_CHUNK_BYTES;
+            tma_load_2d(st, &tmap_a, kb * BK_BYTES, 0, bar);
+            bulk_load(st + C::kABytes + C::kBBytes, g.sfa + (int64_t)kb * CHUNKS * SF_CHUNK_BYTES, sf_bytes, bar);
+        };
+        int stage = 0, kb = kb0;
+        uint32_t phase = 0;
+        if (early) {
+            // the weight's first stages before the wait for the preceding kernel, the activations after it
+            const int n_pre = min(C::kStages, kb1 - kb0);
+            if (elect_one())
+                for (int i = 0; i < n_pre; ++i) load_weight_part(kb0 + i, i);
+            __syncwarp();
+            grid_dependency_wait();
+            if (elect_one())
+                for (int i = 0; i < n_pre; ++i) load_activation_part(kb0 + i, i);
+            __syncwarp();
+            kb = kb0 + n_pre;
+            stage = n_pre;
+            if (stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        for (; kb < kb1; ++kb) {
+            ok = mbar_wait(smem_u32(&empty_bar[0]) + stage * 8, phase ^ 1, abort_flag, WAIT_STAGE_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (elect_one()) {
+                load_weight_part(kb, stage);
+                load_activation_part(kb, stage);
+            }
+            __syncwarp();
+            if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        const uint32_t smem_enc = smem_u32(smem) >> 4;
+        const uint32_t sf_t0 = tmem_base + C::kSfCol0;
+        for (int kb = kb0; kb < kb1; ++kb) {
+            ok = mbar_wait(smem_u32(&full_bar[0]) + stage * 8, phase, abort_flag, WAIT_STAGE_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st_enc = smem_enc + stage * (C::kStageBytes >> 4);
+            const uint32_t a_lo = st_enc | kOperandDescLoFlags;
+            const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+            const uint32_t sfa_lo = st_enc + ((C::kABytes + C::kBBytes) >> 4);
+            const uint32_t sfb_lo = sfa_lo + (C::kSfBytes >> 4);
+            const int nchunk = min(CHUNKS, g.sf_cbg - kb * CHUNKS);
+            if (elect_one()) {
+#pragma unroll
+                for (int j = 0; j < CHUNKS; ++j) {
+                    if (j < nchunk) {
+                        const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
+                        tc_cp_sf(sfa_t, desc64(sfa_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
+                        tc_cp_sf(sfa_t + 8, desc64(sfb_lo + j * (SF_CHUNK_BYTES >> 4), kSfDescHi));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < CHUNKS; ++j) {
+                    if (j < nchunk) {
+                        const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
+                        tc_mma(tmem_base, desc64(a_lo + 2 * j, kOperandDescHi), desc64(b_lo + 2 * j, kOperandDescHi),
+                               Cfg<128>::kIdesc, sfa_t, sfa_t + 8, (j != 0 || kb != kb0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(smem_u32(&empty_bar[0]) + stage * 8);
+            }
+            __syncwarp();
+            if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok && elect_one()) tc_commit(smem_u32(acc_full_bar));
+        __syncwarp();
+    }
+
+    // ---------------- epilogue, part 1 (warps whose tensor-memory lanes hold existing rows) ----------------
+    const int quad = warp & 3;
+    const bool epi = warp >= 2 && quad * 32 < AROWS;
+    const uint32_t t_acc = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int row = quad * 32 + lane;
+    if (epi) {
+        if (early) grid_dependency_wait();   // before tensor scales and bias are read and anything is stored
+        ok = mbar_wait(smem_u32(acc_full_bar), 0, abort_flag, WAIT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int s = 0; s < 4; ++s) {
+                const uint32_t owner = (uint32_t)(s / C::kStepsOwned);
+                if (owner == rank) continue;
+                uint32_t v[32];
+                tc_ld32(t_acc + s * EPI_COLS, v);
+                tc_wait_ld();
+                // slot of this sender in the owner's exchange area: senders in rank order, the owner left out
+                const uint32_t slot = rank < owner ? rank : rank - 1;
+                const uint32_t local = smem_u32(exchange) + slot * C::kSlotBytes +
+                                       (uint32_t)row * (C::kStepsOwned * EPI_COLS * 4) + (uint32_t)(s % C::kStepsOwned) * (EPI_COLS * 4);
+                const uint32_t remote = map_to_cta(local, owner);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) st_cluster_v4(remote + 16 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+        }
+    }
+    // Every thread of every CTA of the cluster, whatever happened above: partial sums delivered and visible.
+    cluster_sync_all();
+    // ---------------- epilogue, part 2: add up the owned steps in rank order, scale, store ----------------
+    if (epi && ok && !*abort_flag) {
+        const float alpha = g.alpha ? __ldg(g.alpha) : __fmul_rn(__ldg(g.tsa), __ldg(g.tsb));
+#pragma unroll 1
+        for (int so = 0; so < C::kStepsOwned; ++so) {
+            const int s = (int)rank * C::kStepsOwned + so;
+            uint32_t own[32];
+            tc_ld32(t_acc + s * EPI_COLS, own);
+            tc_wait_ld();
+            float acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+#pragma unroll
+            for (int src = 0; src < CS; ++src) {
+                if ((uint32_t)src == rank) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(own[i]);
+                } else {
+                    const uint32_t slot = (uint32_t)src < rank ? (uint32_t)src : (uint32_t)src - 1;
+                    const float4* p = reinterpret_cast<const float4*>(exchange + slot * C::kSlotBytes +
+                                                                      row * (C::kStepsOwned * EPI_COLS * 4) + so * (EPI_COLS * 4));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 t = p[j];
+                        acc[4 * j] += t.x; acc[4 * j + 1] += t.y; acc[4 * j + 2] += t.z; acc[4 * j + 3] += t.w;
+                    }
+                }
+            }
+            const int n0 = tn * 128 + s * EPI_COLS;
+            if (row < g.M && n0 < g.N) {
+                uint32_t bits[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) bits[i] = __float_as_uint(acc[i]);
+                float y[32];
+                scale_row32(g, n0, bits, alpha, y);
+                store_row32(g, row, n0, y);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols)
+                     : "memory");
+    }
+}
+
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                                             const float* tsa, const float* tsb, const float* alpha_ptr,
                                                             const void* bias, int bias_dtype, void* out, int out_dtype) {
@@ -1646,6 +1912,57 @@ int launch_gemm(const void* a, const void* b, GemmArgs g, int64_t K, int sms, cu
     return CK_B200_OK;
 }
 
+
+// M <= 64 on clusters that split K (gemm_nvfp4_cluster_kernel).  Returns CK_B200_OK with *taken = false when the
+// shape does not suit it (the caller then takes the other small-M paths).
+template <int AROWS, int CS>
+int launch_gemm_cluster(const void* a, const void* b, GemmArgs g, int64_t K, cudaStream_t stream) {
+    using C = ClusterCfg<AROWS, CS>;
+    auto kernel = gemm_nvfp4_cluster_kernel<AROWS, CS>;
+    {
+        static std::mutex mu;
+        static bool done[64] = {};
+        int dev = 0;
+        CKB_CUDA_OK(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !done[dev]) {
+            CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+            CKB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            if (dev >= 0 && dev < 64) done[dev] = true;
+        }
+    }
+    const int64_t row_bytes = K / 2;
+    CUtensorMap ma, mb;
+    g.a_box_bytes = AROWS * BK_BYTES;
+    if (int rc = make_operand_map(&ma, a, g.M, row_bytes, AROWS)) return rc;
+    if (int rc = cached_operand_map(&mb, b, g.N, row_bytes, 128)) return rc;
+    g.m_tiles = 1;
+    g.n_tiles = (int)ceil_div64(g.N, 128);
+    g.raster_group = 1;
+    g.splits = CS;
+    g.k_per_split = (int)ceil_div64(g.k_iters, CS);
+    g.partial = nullptr;
+    g.tma_store = 0;
+    g.early_weights = g_weights_resident.load() != 0 ? 1 : 0;
+    g_last_splits.store(CS);
+    const cudaError_t err = launch_dependent(kLaunchFamilyGemm, kernel, dim3((unsigned)(g.n_tiles * CS)), dim3(NUM_THREADS),
+                                             C::kSmemBytes, stream, ma, mb, g);
+    g_launches.fetch_add(1);
+    CKB_CUDA_OK(err);
+    return CK_B200_OK;
+}
+
+// Cluster size for a one-tile-row problem: the largest of 4 and 2 whose CTAs are all resident at once (two per SM)
+// and get at least two stages each with no empty rank; 0 = none.
+int choose_cluster_split(int64_t N, int k_iters, int sms) {
+    const int64_t tiles = ceil_div64(N, 128);
+    for (int cs = 4; cs >= 2; cs /= 2) {
+        const int per = (int)ceil_div64(k_iters, cs);
+        if (tiles * cs <= 2ll * sms && per >= 2 && (int64_t)(cs - 1) * per < k_iters) return cs;
+    }
+    return 0;
+}
+
 }  // namespace
 }  // namespace ckb
 
@@ -1663,7 +1980,8 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
                    const float* tensor_scale_a_dev, const float* tensor_scale_b_dev, const float* alpha_dev_or_null,
                    const void* bias_dev_or_null, int bias_dtype, void* out_dev, int out_dtype, int64_t M, int64_t N,
                    int64_t K, SplitScratch scratch, void* stream,
-                   const GatherSpec* gather = nullptr, const FusedQuant* fused = nullptr, int fused_dtype = -1) {
+                   const GatherSpec* gather = nullptr, const FusedQuant* fused = nullptr, int fused_dtype = -1,
+                   bool force_scratch = false) {
     int sms = 0;
     if (int rc = check_device(&sms)) return rc;
     if (!a_dev || !sfa_dev || !b_dev || !sfb_dev || !out_dev)
@@ -1716,10 +2034,15 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     // CTA pairs with 256x256 tiles when the problem has more than one tile row and column; otherwise one CTA per
     // tile, 128x256 (half the operand traffic per flop of 128x128) unless N is a single 128-column tile
     // variant 5 = the short-row configuration where it applies (M <= 64), the automatic choice elsewhere
-    // (automatic: from 64 such tiles up - measured on M = 16: 128 <= N <= 2560 at K = 4096 is 3-4 % faster on 128-column
-    // tiles with their split-K, N >= 4096 equal or faster on 64-column tiles)
-    const bool skinny = M <= 64 && (variant == 5 || (variant == 0 && g_gemm_skinny.load() != 0 && N >= 4096));
-    if (variant == 0 || variant == 5) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
+    // (automatic: when the 64-column tiles alone fill the SMs, so that K is not split - measured on M = 16: with fewer
+    // tiles the 128-column configuration and its smaller number of K splits is equal or 3-4 % faster)
+    const bool skinny = M <= 64 && (variant == 5 || (variant == 0 && g_gemm_skinny.load() != 0 && N >= 64ll * sms));
+    // variant 6 = K split over a thread-block cluster, partial sums exchanged through shared memory (M <= 64, 16-byte
+    // aligned rows of packed K)
+    int cluster_split = 0;
+    if (M <= 64 && K % 32 == 0 && (variant == 6 || (variant == 0 && g_gemm_cluster_split.load() != 0)) && !force_scratch)
+        cluster_split = choose_cluster_split(N, g.k_iters, sms);
+    if (variant == 0 || variant == 5 || variant == 6) variant = (M > 128 && N > 128) ? 3 : (N > 128) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
     if ((uintptr_t)scratch.partial & 15)
         return fail(CK_B200_ERR_INVALID_ARGUMENT, "scaled_mm_nvfp4: workspace must be 16-byte aligned");
@@ -1745,6 +2068,10 @@ int scaled_mm_impl(const void* a_dev, const void* sfa_dev, const void* b_dev, co
     if (variant == 3 && M > 128) return launch_gemm_pair<128>(a_dev, b_dev, g, K, s);
     if (variant == 2 && M > 128) return launch_gemm<256>(a_dev, b_dev, g, K, sms, s, scratch);
     // one short tile row: 64-column tiles, two CTAs per SM (every SM streams its share of the weight from the start)
+    if (cluster_split == 2 && M <= 32) return launch_gemm_cluster<32, 2>(a_dev, b_dev, g, K, s);
+    if (cluster_split == 2 && M <= 64) return launch_gemm_cluster<64, 2>(a_dev, b_dev, g, K, s);
+    if (cluster_split == 4 && M <= 32) return launch_gemm_cluster<32, 4>(a_dev, b_dev, g, K, s);
+    if (cluster_split == 4 && M <= 64) return launch_gemm_cluster<64, 4>(a_dev, b_dev, g, K, s);
     if (skinny && M <= 32) return launch_gemm<64, 0, 32>(a_dev, b_dev, g, K, sms, s, scratch);
     if (skinny && M <= 64) return launch_gemm<64, 0, 64>(a_dev, b_dev, g, K, sms, s, scratch);
     // one tile row: 128-column tiles give the most work items, and split-K (with scratch) fills the remaining SMs
@@ -1994,7 +2321,8 @@ extern "C" int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const v
     if (int rc = static_scratch_address(&scratch)) return rc;
     return scaled_mm_impl(a_dev, sfa_dev, b_dev, sfb_dev, tensor_scale_a_dev, tensor_scale_b_dev, alpha_dev_or_null,
                           bias_dev_or_null, bias_dtype, out_dev, out_dtype, M, N, K,
-                          scratch_from_workspace(scratch, kStaticScratchBytes), stream);
+                          scratch_from_workspace(scratch, kStaticScratchBytes), stream, nullptr, nullptr, -1,
+                          /*force_scratch=*/true);   // this entry point's path is the one through its scratch array
 }
 
 extern "C" int ck_b200_read_gemm_counters(long long* out5) {

@@ -257,7 +257,8 @@ int ck_b200_read_gemm_counters(long long* out5);
  * environment switches, comfy_kitchen/backends/cuda/__init__.py:212-215, do not touch this path). */
 #define CK_B200_TUNE_QUANT_VARIANT 0 /* 0 = IEEE divisions, 1 = reciprocal bracket + exact fallback, 2 = one-round residual correction (default) */
 #define CK_B200_TUNE_GEMM_VARIANT 1  /* GEMM tile configuration; 0 = automatic, 1 = 128x128 one CTA, 2 = 128x256 one CTA, 3 = 256x256 CTA
-                                        pair, 4 = the same with half-width stages, 5 = 128x64 with two CTAs per SM where M <= 64 */
+                                        pair, 4 = the same with half-width stages, 5 = 128x64 with two CTAs per SM where M <= 64,
+                                        6 = K split over a cluster where M <= 64 */
 #define CK_B200_TUNE_GEMM_DEBUG 2    /* non-zero: the counting build of the GEMM kernels runs; 1 = its first CTA also prints the
                                         cycles its roles spent waiting, 2 = counters only (ck_b200_read_gemm_counters) */
 #define CK_B200_TUNE_DEPENDENT_LAUNCH 3 /* non-zero (default): kernels are launched with programmatic stream
@@ -279,15 +280,17 @@ int ck_b200_read_gemm_counters(long long* out5);
 #define CK_B200_TUNE_QUANT_ONCHIP 10 /* non-zero (default): quantize_nvfp4 of a 16-bit input of up to about 32 MB with rows and
                                        columns multiples of 128 asks for the whole input at once (asynchronous copies into
                                        shared memory) instead of walking it with a register ring */
-#define CK_B200_TUNE_GEMM_SKINNY 11 /* non-zero (default): a GEMM with M <= 64 and N >= 4096 runs on 64-column tiles with two CTAs per SM
-                                      (twice the CTAs of the 128-column configuration, each with a short ring); GEMM variant 5
-                                      forces that configuration for every M <= 64 */
+#define CK_B200_TUNE_GEMM_SKINNY 11 /* non-zero (default): a GEMM with M <= 64 and at least one 64-column tile per SM (N >= 64 x SMs) runs
+                                      on 64-column tiles with two CTAs per SM (twice the CTAs of the 128-column configuration,
+                                      each with a short ring); GEMM variant 5 forces that configuration for every M <= 64 */
 #define CK_B200_TUNE_WEIGHTS_RESIDENT 12 /* A promise by the caller, off by default: when a GEMM with M <= 128 is enqueued, nothing that is
                                            still in flight on the GPU writes its B operand or B scales (weights quantized when the
                                            model was loaded, and synchronised since).  The kernel then requests the first stages of the
                                            weight BEFORE it waits for the preceding kernel of the stream, so a stack of small-M layers
                                            streams layer i+1's weight under layer i's tail.  Activations, their scales, tensor scales,
                                            bias and every store still wait. */
+#define CK_B200_TUNE_GEMM_CLUSTER_SPLITK 13 /* non-zero: a GEMM with M <= 64 splits K over a thread-block cluster of 2 or 4 CTAs that exchange
+                                              their partial sums through shared memory (one launch, no scratch); also GEMM variant 6 */
 int ck_b200_set_tuning(int key, int value);
 
 #ifdef __cplusplus

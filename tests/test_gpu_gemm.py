@@ -22,7 +22,8 @@ def ckb():
     return m
 
 
-@pytest.fixture(params=[1, 2, 3, 4, 5], ids=["bn128", "bn256", "pair256", "pair256-k128", "short-rows-bn64"])
+@pytest.fixture(params=[1, 2, 3, 4, 5, 6],
+                ids=["bn128", "bn256", "pair256", "pair256-k128", "short-rows-bn64", "short-rows-cluster-splitk"])
 def variant(request, ckb):
     prev = ckb.set_tuning(1, request.param)
     yield request.param
@@ -197,14 +198,15 @@ def test_split_k_repeats_and_graph_replays(mnk, ckb):
 
 
 SHORT_ROWS = [(16, 10240, 4096), (64, 10240, 4096), (1, 12288, 1024), (33, 10248, 4096), (16, 4096, 10240),
-              (64, 4096, 10240), (48, 72, 96), (8, 8, 32)]
+              (64, 4096, 10240), (48, 72, 96), (8, 8, 32), (16, 2560, 4096), (8, 128, 1024), (40, 136, 2080)]
 
 
 @pytest.mark.parametrize("mnk", SHORT_ROWS, ids=lambda s: "x".join(map(str, s)))
 def test_short_row_tiles_match_128_column_tiles(mnk, ckb):
     """M <= 64 on 64-column tiles with two CTAs per SM (a tile reads its scales from half of a 128-row band's chunk
-    in tensor memory): bit-identical to the 128-column tiles whenever both cut K into the same number of splits,
-    within the GEMM tolerance otherwise; N tails and single-tile problems included."""
+    in tensor memory), and with K split over a thread-block cluster that adds the partial sums up through shared
+    memory: bit-identical to the 128-column tiles whenever both cut K into the same number of splits, within the
+    GEMM tolerance otherwise; N tails and single-tile problems included."""
     from comfy_kitchen_b200 import _lib
     M, N, K = mnk
     x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=3 * M + N + K)
@@ -213,14 +215,15 @@ def test_short_row_tiles_match_128_column_tiles(mnk, ckb):
     try:
         ref = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
         splits_ref = _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
-        ckb.set_tuning(1, 5)
-        for _ in range(3):
-            y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
-            splits = _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
-            if splits == splits_ref:
-                assert torch.equal(y, ref)
-            else:
-                assert rel_rms(y[:M].float(), ref[:M].float()) <= 1e-3
+        for v in (5, 6):
+            ckb.set_tuning(1, v)
+            for _ in range(3):
+                y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, bias=bias)
+                splits = _lib.load().ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
+                if splits == splits_ref:
+                    assert torch.equal(y, ref), f"variant {v}"
+                else:
+                    assert rel_rms(y[:M].float(), ref[:M].float()) <= 1e-3, f"variant {v}"
     finally:
         ckb.set_tuning(1, prev)
     assert ckb.read_device_status() == 0
@@ -228,7 +231,8 @@ def test_short_row_tiles_match_128_column_tiles(mnk, ckb):
 
 @pytest.mark.parametrize("mnk", [(16, 10240, 4096), (64, 4096, 10240), (128, 4096, 4096), (1, 4096, 4096)],
                          ids=lambda s: "x".join(map(str, s)))
-def test_weight_loads_ahead_of_the_preceding_kernel(mnk, ckb):
+@pytest.mark.parametrize("variant_under_promise", [0, 5, 6], ids=["auto", "bn64", "cluster"])
+def test_weight_loads_ahead_of_the_preceding_kernel(mnk, variant_under_promise, ckb):
     """With the caller's promise that weights are resident, a small-M GEMM asks for its weight before it waits for the
     preceding kernel of the stream.  Activations, their scales and the tensor scale are produced by the kernels right
     before it on the same stream with no synchronisation in between, so the test fails if anything but the weight is
@@ -252,6 +256,7 @@ def test_weight_loads_ahead_of_the_preceding_kernel(mnk, ckb):
         return outs
 
     torch.cuda.synchronize()      # the promise: the weights above are complete and stay untouched
+    prev_variant = ckb.set_tuning(1, variant_under_promise)
     want = []
     for xj in xs:
         x.copy_(xj)
@@ -278,6 +283,7 @@ def test_weight_loads_ahead_of_the_preceding_kernel(mnk, ckb):
             for o, wnt in zip(outs, want[j]):
                 assert torch.equal(o, wnt)
     finally:
+        ckb.set_tuning(1, prev_variant)
         ckb.promise_resident_weights(prev)
     assert ckb.read_device_status() == 0
 
