@@ -548,7 +548,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     // overwrites scales that the MMAs issued just before it still read)
 #pragma unroll
                     for (int j = 0; j < CHUNKS; ++j) {
-                        if (j < nchunk && !(DBG && (g.debug & 4))) {   // experiment: timing without the scale copies
+                        if (j < nchunk) {
                             const uint32_t sfa_t = sf_t0 + (j >> 1) * C::kSfRegionCols + (j & 1) * 4;
                             const uint32_t sfb_t =
                                 sf_t0 + (j >> 1) * C::kSfRegionCols + C::kSfaColsHalf + (j & 1) * 4 * C::kBands;
@@ -1048,7 +1048,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                 } else if (elect_one()) {
 #pragma unroll
                     for (int j = 0; j < kChunks; ++j) {
-                        if (j < nchunk && !(DBG && (g.debug & 4))) {   // experiment: timing without the scale copies
+                        if (j < nchunk) {
                             const uint32_t sf_r = sf_t0 + (region0 + (j >> 1)) * kSfRegion2;
                             const uint32_t sfa_t = sf_r + (j & 1) * 4;
                             const uint32_t sfb_t = sf_r + 8 + (j & 1) * 8;
