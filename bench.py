@@ -767,25 +767,34 @@ def small_m_sweep(B: Bench):
 def eager_latency(B: Bench):
     """Wall-clock time per forward of a 4096 -> 4096 NVFP4 layer called eagerly (no CUDA graph), dynamic activation
     scale, as the reference layer is used (samples/nvfp4_linear.py:77-80): host work (Python, ctypes, tensor-map
-    encoding, launches) plus device work, averaged over 200 back-to-back calls followed by one synchronise."""
+    encoding, launches) plus device work, averaged over 200 back-to-back calls followed by one synchronise (best of three such runs)."""
     import comfy_kitchen_b200 as ckb
     torch = B.torch
     g = torch.Generator(device=B.dev).manual_seed(11)
     w = (torch.randn((4096, 4096), generator=g, device=B.dev) * 0.02).to(torch.bfloat16)
     lin = ckb.NVFP4Linear.from_float(w, None)
     out = []
-    for m in (1, 64, 512):
-        x = torch.randn((m, 4096), generator=g, device=B.dev, dtype=torch.bfloat16)
+    xs = {m: torch.randn((m, 4096), generator=g, device=B.dev, dtype=torch.bfloat16) for m in (1, 64, 512)}
+    for x in xs.values():      # every shape and both forms once through before anything is timed
+        for f in (lin.forward, lin.forward_unfused):
+            for _ in range(50):
+                f(x)
+    torch.cuda.synchronize()
+    for m, x in xs.items():
         rec = {"M": m}
         for name, f in (("one_call_us", lin.forward), ("three_operators_us", lin.forward_unfused)):
-            for _ in range(20):
-                f(x)
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            for _ in range(200):
-                f(x)
-            torch.cuda.synchronize()
-            rec[name] = (time.perf_counter() - t0) / 200 * 1e6
+            best = None
+            for _ in range(3):      # best of three runs of 200 forwards: host jitter is one-sided
+                for _ in range(20):
+                    f(x)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(200):
+                    f(x)
+                torch.cuda.synchronize()
+                t = (time.perf_counter() - t0) / 200 * 1e6
+                best = t if best is None else min(best, t)
+            rec[name] = best
         out.append(rec)
     return {"layer": "NVFP4Linear 4096 -> 4096, bf16, input_scale=None", "per_forward": out,
             "one_call": "ck_b200_linear_nvfp4 (dynamic quantizer, GEMM: 2-3 launches from one library call)",
