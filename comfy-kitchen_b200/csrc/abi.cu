@@ -19,7 +19,7 @@ std::atomic<int> g_gemm_cluster_split{0};
 std::atomic<int> g_linear_fused{0};
 std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
-std::atomic<int> g_dynamic_fused_max_mb{64};
+std::atomic<int> g_dynamic_fused_max_mb{128};
 std::atomic<int> g_dynamic_smem{1};
 std::atomic<int> g_quant_onchip{1};
 

@@ -380,34 +380,37 @@ __device__ __forceinline__ float raw_amax(const typename Input<DT>::Raw& r) {
     }
 }
 
-// Maximum of |x| over the part of units [pos, end) of the flat unit sequence that this lane owns.
+// Maximum of |x| over the part of units [pos, end) of the flat unit sequence that this lane owns.  The range is
+// walked from its end to its start: the quantizing pass that follows walks it from the start, so what this pass
+// read last - the part of the range most likely to be still in L2 - is what that pass reads first.
 template <int DT>
 __device__ __forceinline__ float range_amax(const QuantArgs& a, long long pos, long long end, int lane) {
     using In = Input<DT>;
     constexpr int kUnitBytes = 64 * In::kBytes;
     float m = 0.0f;
     const int sub = lane & 7;
-    while (pos < end) {
-        const int gi = (int)(pos / a.sf_cbg);
-        const int u0 = (int)(pos - (long long)gi * a.sf_cbg);
-        const int u1 = (int)min((long long)a.sf_cbg, (long long)u0 + (end - pos));
+    while (end > pos) {
+        const int gi = (int)((end - 1) / a.sf_cbg);
+        const long long base = (long long)gi * a.sf_cbg;
+        const int u1 = (int)(end - base);
+        const int u0 = (int)(max(pos, base) - base);
         const int group = a.row_groups - 1 - gi;
         const int r = (group >> 5) * 128 + (group & 31) + 32 * (lane >> 3);
         if (r < a.rows) {
             const char* p = (const char*)a.x + ((int64_t)r * a.cols + sub * 8) * In::kBytes;
             // units whose eight columns of this lane lie inside the row (cols is a multiple of 8 on this path)
             const int u_in = min(u1, (a.cols - sub * 8 + 63) / 64);
-            int u = u0;
-            for (; u + 4 <= u_in; u += 4) {
-                const typename In::Raw r0 = In::load_vec(p + (int64_t)u * kUnitBytes),
-                                       r1 = In::load_vec(p + (int64_t)(u + 1) * kUnitBytes),
-                                       r2 = In::load_vec(p + (int64_t)(u + 2) * kUnitBytes),
-                                       r3 = In::load_vec(p + (int64_t)(u + 3) * kUnitBytes);
+            int u = u_in;
+            for (; u - 4 >= u0; u -= 4) {
+                const typename In::Raw r0 = In::load_vec(p + (int64_t)(u - 1) * kUnitBytes),
+                                       r1 = In::load_vec(p + (int64_t)(u - 2) * kUnitBytes),
+                                       r2 = In::load_vec(p + (int64_t)(u - 3) * kUnitBytes),
+                                       r3 = In::load_vec(p + (int64_t)(u - 4) * kUnitBytes);
                 m = fmaxf(fmaxf(m, fmaxf(raw_amax<DT>(r0), raw_amax<DT>(r1))), fmaxf(raw_amax<DT>(r2), raw_amax<DT>(r3)));
             }
-            for (; u < u_in; ++u) m = fmaxf(m, raw_amax<DT>(In::load_vec(p + (int64_t)u * kUnitBytes)));
+            for (; u > u0; --u) m = fmaxf(m, raw_amax<DT>(In::load_vec(p + (int64_t)(u - 1) * kUnitBytes)));
         }
-        pos += u1 - u0;
+        end = base + u0;
     }
     return m;
 }
@@ -856,8 +859,8 @@ extern "C" int ck_b200_quantize_nvfp4_dynamic(const void* x_dev, int x_dtype, fl
     const int64_t sf_cbg = round_up64(pcol / 16, 4) / 4;
     const int64_t in_bytes = rows * cols * (x_dtype == CK_B200_DTYPE_F32 ? 4 : 2);
     const bool vec = (cols % 8 == 0) && (((uintptr_t)x_dev & 15) == 0);
-    // one launch while x fits half of the L2 (the second pass then reads it from there; a stream of 113 MB was
-    // measured to be gone from the 126 MB L2 by then) and the one-wave geometry applies;
+    // one launch while x is about the size of the L2 or smaller (the first pass walks each warp's range backwards, so
+    // the second pass starts on what L2 still holds) and the one-wave geometry applies;
     // otherwise the reduction kernel, the scale and the quantizer as separate launches: same bits either way
     const bool one_launch = sync_dev && vec && sf_cbg % 2 == 0 && prow > 0 && pcol > 0 && g_quant_variant.load() == 2 &&
                             in_bytes <= (int64_t)g_dynamic_fused_max_mb.load() * 1000000ll &&

@@ -207,11 +207,12 @@ int ck_b200_dynamic_scale_nvfp4(const void* x_dev, int x_dtype, int64_t numel, f
  * caller gives none (comfy_kitchen/tensor/nvfp4.py:53-84: scale = amax(|x|) / (448*6) in x's dtype, then
  * ck.quantize_nvfp4(x, scale)).  Same outputs, bit for bit, as ck_b200_dynamic_scale_nvfp4 followed by
  * ck_b200_quantize_nvfp4; scale_out_dev receives the float32 scale (the GEMM's tensor_scale_a).
- * While x fits half of the L2 (CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB, default 64) this is ONE kernel launch: every warp takes the
- * maximum over the part of x it will quantize, the blocks meet at a grid-wide counter, then quantize from L2 - or,
- * up to about 32 MB of 16-bit input, from shared memory, where the first pass parked it - the second read of x from
- * HBM is gone.  Larger or oddly shaped inputs (columns not a multiple of 128, unaligned base)
- * take the separate kernels inside the same call.
+ * While x is about the size of the L2 or smaller (CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB, default 128) this is ONE kernel launch:
+ * every warp takes the maximum over the part of x it will quantize, walking it backwards, the blocks meet at a grid-wide
+ * counter, then every warp quantizes its part forwards - from what L2 still holds of it, or, up to about 32 MB of 16-bit
+ * input, from shared memory, where the first pass parked it: the second read of x from HBM is gone or shortened.
+ * Larger or oddly shaped inputs (an odd number of 64-column units, unaligned base) take the separate kernels inside
+ * the same call.
  *   sync_dev   16 bytes, 16-byte aligned, zero before the first call; the kernel leaves them zero.  Calls that share
  *              them must be ordered on one stream.  NULL selects the separate kernels.
  * The meeting point is a bounded wait (about a second): if it runs out, the blocks record code 8 in the status word
@@ -270,8 +271,9 @@ int ck_b200_read_gemm_counters(long long* out5);
 #define CK_B200_TUNE_QUANT_SYNC_TEST 6 /* tests only: n > 0 makes the dynamic quantizer wait for n blocks that do not
                                         exist and give up after about 0.1 s (the wait then runs out by design) */
 #define CK_B200_TUNE_DYNAMIC_FUSED_MAX_MB 7 /* largest input, in 10^6 bytes, that ck_b200_quantize_nvfp4_dynamic handles
-                                             in one launch (default 64: a stream of that size survives in the 126 MB L2
-                                             until it is read again; 113 MB was measured not to) */
+                                             in one launch (default 128; measured with the backward / forward walk: 57 MB
+                                             26 us against 33 with separate kernels, 113 MB 51 against 57, 336 MB 148
+                                             against 136) */
 #define CK_B200_TUNE_DYNAMIC_SMEM 8 /* non-zero (default): inputs of up to about 32 MB with rows and columns multiples of
                                      128 stay in shared memory between the two phases of ck_b200_quantize_nvfp4_dynamic */
 #define CK_B200_TUNE_GEMM_MAX_PAIRS 9 /* n > 0: the CTA-pair GEMM (and its all-gather form) launches at most n pairs of CTAs
