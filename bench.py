@@ -931,6 +931,9 @@ def run_ours(args, wl):
     one_call = args.fused_linear
     if one_call:
         ckb.set_tuning(4, 1)
+    for kv in args.tune:      # A/B runs of one library switch: --tune KEY=VALUE (ck_b200_set_tuning)
+        key, value = kv.split("=")
+        ckb.set_tuning(int(key), int(value))
 
     M = wl["M"]
     pad_m = M % 16 != 0
@@ -1098,17 +1101,17 @@ def run_ours(args, wl):
         rq, _ = B.graphed(repeated(one_quant(i)))
         tg = B.timed(rg, args.steps) / (args.steps * R)
         tq = B.timed(rq, args.steps) / (args.steps * R)
-        # the same quantizer launch through the register-ring kernels (inputs of up to ~32 MB otherwise go through
-        # shared memory with the whole input in flight)
-        prev_onchip = ckb.set_tuning(10, 0)
+        # the same quantizer launch through the kernel that parks inputs of up to ~32 MB in shared memory with the whole
+        # input in flight (off by default: same time alone, and it cannot run beside a GEMM's CTAs)
+        prev_onchip = ckb.set_tuning(10, 1)
         rq2, _ = B.graphed(repeated(one_quant(i)))
-        tq_ring = B.timed(rq2, args.steps) / (args.steps * R)
+        tq_chip = B.timed(rq2, args.steps) / (args.steps * R)
         ckb.set_tuning(10, prev_onchip)
         B.graphs.clear()
         n_local = lin.local_rows
         per_linear.append({"linear": name, "K": k, "N_local": n_local, "quantize_us": tq * 1e3, "gemm_us": tg * 1e3,
                            "gemm_tflops": 2.0 * M * n_local * k / (tg * 1e-3) / 1e12,
-                           "quantize_gbs": M * k * 2.5625 / (tq * 1e-3) / 1e9, "quantize_ring_kernels_us": tq_ring * 1e3})
+                           "quantize_gbs": M * k * 2.5625 / (tq * 1e-3) / 1e9, "quantize_onchip_kernel_us": tq_chip * 1e3})
         gemm_ms += tg
         quant_ms += tq
         gemm_fl += 2.0 * M * n_local * k
@@ -1376,6 +1379,8 @@ def main():
     ap.add_argument("--e2e-serial", action="store_true",
                     help="end-to-end arm: one host<->device transfer at a time instead of overlapping the two directions")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of one CUDA graph per step")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="set a library tuning switch (ck_b200_set_tuning) before anything runs; may be repeated")
     ap.add_argument("--kernels-only", action="store_true",
                     help="launch each kernel of the path twice on the workload's shapes and exit (a target for ncu captures)")
     args = ap.parse_args()

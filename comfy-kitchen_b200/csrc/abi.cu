@@ -21,7 +21,7 @@ std::atomic<int> g_quant_flat{12};
 std::atomic<int> g_quant_sync_test{0};
 std::atomic<int> g_dynamic_fused_max_mb{128};
 std::atomic<int> g_dynamic_smem{1};
-std::atomic<int> g_quant_onchip{1};
+std::atomic<int> g_quant_onchip{0};
 
 char* last_error_buffer() {
     static thread_local char buf[512] = {0};

@@ -279,9 +279,11 @@ int ck_b200_read_gemm_counters(long long* out5);
 #define CK_B200_TUNE_GEMM_MAX_PAIRS 9 /* n > 0: the CTA-pair GEMM (and its all-gather form) launches at most n pairs of CTAs
                                        instead of one per pair of SMs, so that two such kernels on two streams run side by
                                        side; 0 (default) = all */
-#define CK_B200_TUNE_QUANT_ONCHIP 10 /* non-zero (default): quantize_nvfp4 of a 16-bit input of up to about 32 MB with rows and
-                                       columns multiples of 128 asks for the whole input at once (asynchronous copies into
-                                       shared memory) instead of walking it with a register ring */
+#define CK_B200_TUNE_QUANT_ONCHIP 10 /* non-zero: quantize_nvfp4 of a 16-bit input of up to about 32 MB with rows and columns
+                                       multiples of 128 asks for the whole input at once (asynchronous copies into shared
+                                       memory) instead of walking it with a register ring.  Off by default: alone it takes
+                                       the same time, and its 72 KB of shared memory per block keep it from running beside
+                                       a GEMM's CTAs (a step whose quantizers overlap its GEMMs is 3.7 % slower with it) */
 #define CK_B200_TUNE_GEMM_SKINNY 11 /* non-zero (default): a GEMM with M <= 64 and at least one 64-column tile per SM (N >= 64 x SMs) runs
                                       on 64-column tiles with two CTAs per SM (twice the CTAs of the 128-column configuration,
                                       each with a short ring); GEMM variant 5 forces that configuration for every M <= 64 */

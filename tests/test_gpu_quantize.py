@@ -208,14 +208,14 @@ def test_sweep_shapes_row_slices_vs_oracle(mk, ckb, oracle):
     assert np.float32(tsf) == np.float32(float((x.abs().amax() / 2688.0).float()))    # bf16 arithmetic, like the layout
     q, sf = ckb.quantize_nvfp4(x, ts)
     if M * K * 2 <= 33_000_000:
-        # this size is quantized from shared memory with the whole input in flight; the register-ring kernels must
-        # give the same bytes
-        prev = ckb.set_tuning(10, 0)
+        # this size can also be quantized from shared memory with the whole input in flight (off by default); that
+        # kernel must give the bytes of the register-ring kernels
+        prev = ckb.set_tuning(10, 1)
         try:
-            q_ring, sf_ring = ckb.quantize_nvfp4(x, ts)
+            q_chip, sf_chip = ckb.quantize_nvfp4(x, ts)
         finally:
             ckb.set_tuning(10, prev)
-        assert torch.equal(q, q_ring) and torch.equal(sf.view(torch.uint8), sf_ring.view(torch.uint8))
+        assert torch.equal(q, q_chip) and torch.equal(sf.view(torch.uint8), sf_chip.view(torch.uint8))
     y = ckb.dequantize_nvfp4(q, ts, sf, torch.bfloat16)
     sfu = sf.view(torch.uint8)
     for r0 in sorted({0, (M // 2) // 128 * 128, M - 256}):
