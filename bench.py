@@ -378,19 +378,22 @@ class StepPlan:
         if self.fused and not (self.equal_shards and M > 128 and all(n // world > 128 for _, _, n in wl["linears"])):
             self.fused = False
             self.declined = "the fused kernel wants equal shards wider than 128 columns and more than 128 rows"
-        # The fused path maps every rank's output matrices into every process.  With 18 GB of peer mappings (the
-        # Wan workload on 8 GPUs: 7 peers x 2.6 GB) its stores ran at 96 GB/s per rank; with 1.8 GB (Flux, 8 GPUs) and
-        # 2.6 GB (Wan, 2 GPUs) at 420-480 GB/s.  Large footprints therefore take the NCCL path, and the line says so.
-        peer_bytes = (world - 1) * sum(M * n * 2 for _, _, n in wl["linears"])
-        if self.fused and peer_bytes > (B.args.peer_map_limit_gib << 30):
-            self.fused = False
-            self.declined = (f"{peer_bytes / 2**30:.1f} GiB of peer-mapped output matrices per rank: NCCL all-gather "
-                             "instead")
-        self.use_graph = B.use_graph and (not B.distributed or self.fused)
-        self.half_pairs = max(1, int(ckb._lib.load().ck_b200_query(ckb._lib.QUERY_SM_COUNT)) // 4)   # half of the CTA pairs
+        # The fused path maps every rank's output matrices into every process, and the library bounds those mappings
+        # (PeerGroup.map_limit_bytes: with 16.8 GiB mapped - the Wan workload on 8 GPUs - the stores ran at 202 GB/s per
+        # rank, with up to 7.7 GiB at 470-580).  A workload is taken fused as a whole or not at all, and the line says so.
         self.peers = None
         if self.fused:
-            self.peers = ckb.PeerGroup(B.dev)
+            self.peers = ckb.PeerGroup(B.dev, map_limit_bytes=B.args.peer_map_limit_gib << 30)
+            per_rank = sum(M * n * 2 for _, _, n in wl["linears"])
+            if not self.peers.fits(per_rank):
+                self.fused = False
+                self.declined = (f"{(world - 1) * per_rank / 2**30:.1f} GiB of peer-mapped output matrices per rank is above "
+                                 f"the library's limit of {B.args.peer_map_limit_gib} GiB: NCCL all-gather instead")
+                self.peers.close()
+                self.peers = None
+        self.use_graph = B.use_graph and (not B.distributed or self.fused)
+        self.half_pairs = max(1, int(ckb._lib.load().ck_b200_query(ckb._lib.QUERY_SM_COUNT)) // 4)   # half of the CTA pairs
+        if self.fused:
             for lin in self.layers:
                 lin.bind(self.peers, M)
 

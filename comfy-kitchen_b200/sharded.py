@@ -102,18 +102,34 @@ class PeerMemory:
 
 
 class PeerGroup:
-    """The ranks of one node as seen by the fused kernels: mapped memory plus a stream-ordered barrier."""
+    """The ranks of one node as seen by the fused kernels: mapped memory plus a stream-ordered barrier.
 
-    def __init__(self, device: torch.device, group=None, ops=None):
+    ``map_limit_bytes`` bounds the other ranks' memory that layers bound to this group map into this process.  The
+    fused all-gather stores into those mappings, which the GPU translates in 2 MiB pages through a cache of limited
+    reach: measured on B200s, 7.7 GiB mapped per rank (4 GPUs) takes the stores at 584 GB/s per rank, 16.8 GiB (8 GPUs)
+    at 202 GB/s - five times slower than the NCCL all-gather of the same blocks.  ``ShardedNVFP4Linear.bind`` therefore
+    declines (with a warning) what would pass the limit, and such a layer's ``fused`` takes the NCCL form."""
+
+    DEFAULT_MAP_LIMIT_BYTES = 12 << 30
+
+    def __init__(self, device: torch.device, group=None, ops=None, map_limit_bytes: int | None = None):
         self.device, self.group = torch.device(device), group
         self.flags = PeerMemory(256, self.device, group, ops)
         self.ops, self.world, self.rank = self.flags.ops, self.flags.world, self.flags.rank
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.blocks: list[PeerMemory] = [self.flags]
+        self.map_limit_bytes = self.DEFAULT_MAP_LIMIT_BYTES if map_limit_bytes is None else int(map_limit_bytes)
+        self.mapped_bytes = 0      # bytes of the other ranks' blocks mapped into this process through this group
+
+    def fits(self, nbytes_per_rank: int) -> bool:
+        """Whether blocks of ``nbytes_per_rank`` more on every rank keep this process's peer mappings within the limit
+        (the same answer on every rank: it depends on sizes only)."""
+        return self.mapped_bytes + (self.world - 1) * int(nbytes_per_rank) <= self.map_limit_bytes
 
     def alloc(self, nbytes: int) -> PeerMemory:
         m = PeerMemory(nbytes, self.device, self.group, self.ops)
         self.blocks.append(m)
+        self.mapped_bytes += (self.world - 1) * int(nbytes)
         return m
 
     def barrier(self) -> None:
@@ -235,14 +251,26 @@ class ShardedNVFP4Linear:
         sizes = {b - a for a, b in (shard_rows(self.out_features, self.world, r) for r in range(self.world))}
         if len(sizes) != 1:
             raise ValueError("the fused all-gather needs equal shards")
-        self.peers = peers
-        self._out_mem = peers.alloc(m * self.out_features * 2)
         self._out_rows, self._out_dtype = m, dtype
+        nbytes = m * self.out_features * 2
+        if not peers.fits(nbytes):
+            # beyond the reach of the GPU's translation cache for peer memory the stores collapse (PeerGroup): this
+            # layer keeps the library collective, and fused() says so once
+            import warnings
+            warnings.warn(f"ShardedNVFP4Linear.bind: {(peers.mapped_bytes + (peers.world - 1) * nbytes) / 2**30:.1f} GiB of peer "
+                          f"mappings would pass the limit of {peers.map_limit_bytes / 2**30:.1f} GiB; this layer uses the "
+                          "NCCL all-gather instead of the fused epilogue", RuntimeWarning, stacklevel=2)
+            self.peers, self._out_mem, self.out_full = None, None, None
+            return None
+        self.peers = peers
+        self._out_mem = peers.alloc(nbytes)
         self.out_full = self._out_mem.tensor((m, self.out_features), dtype)
         return self.out_full
 
     def fused_from_quantized(self, qx: torch.Tensor, sfx: torch.Tensor, ts_x: torch.Tensor, rows: int) -> torch.Tensor:
         assert rows == self._out_rows, "bind() fixed the number of rows"
+        if getattr(self, "out_full", None) is None:      # bind() declined: the same matrix through the library collective
+            return self.gather(self.local_from_quantized(qx, sfx, ts_x, rows))
         self.ops.scaled_mm_nvfp4_all_gather(qx, self.qweight, ts_x, self.weight_scale, sfx, self.weight_block_scale,
                                             self._out_mem.ptrs, self.rank, out_dtype=self._out_dtype, bias=self.bias,
                                             rows=rows)

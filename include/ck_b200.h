@@ -107,9 +107,13 @@ int ck_b200_scaled_mm_nvfp4_static_scratch(const void* a_dev, const void* sfa_de
 /*
  * scaled_mm_nvfp4 of a column-parallel (N-sharded) linear fused with the all-gather of its output: the calling rank
  * computes columns [rank*N_local, (rank+1)*N_local) of the [M, world*N_local] result and the kernel's epilogue
- * stores every finished tile into that column block of EVERY rank's matrix - its own through TMA, the others'
- * through stores to peer memory over NVLink - so no separate collective runs afterwards.  No counterpart in the
- * reference, which is single-GPU (the multi-GPU form of comfy_kitchen/tensor/nvfp4.py:212-260).
+ * stores every finished tile into that column block of EVERY rank's matrix (bulk copies of 512-byte tile rows out of
+ * shared memory, to its own memory and to peer memory over NVLink), so no separate collective runs afterwards.  No
+ * counterpart in the reference, which is single-GPU (the multi-GPU form of comfy_kitchen/tensor/nvfp4.py:212-260).
+ * Keep the peers' memory mapped into one process within about 12 GiB: peer memory is translated in 2 MiB pages through
+ * a cache of limited reach; measured on B200s, 7.7 GiB mapped per rank takes these stores at 584 GB/s per rank, 16.8 GiB
+ * at 202 GB/s (five times slower than an NCCL all-gather of the same blocks).  The Python layer enforces that bound
+ * (PeerGroup.map_limit_bytes); a native caller has to.
  *
  *   out_ptrs   host array of `world` pointers: out_ptrs[r] is rank r's [M, world*N_local] 16-bit matrix as
  *              addressable from this device (own memory for r == rank; ck_b200_peer_open mappings otherwise)

@@ -91,6 +91,25 @@ def _worker(rank, world, port, n_out, result_dir):
         assert torch.equal(lin2(x), y) and calls == [(48, 128)]
         lin3 = ckb.ShardedNVFP4Linear(w, bias, ops=ops2, input_scale=ops.dynamic_scale_nvfp4(x))
         assert torch.equal(lin3(x), y) and len(calls) == 1     # a stored scale is used as it is
+        # a group whose peer-mapping limit the layer's output matrices would pass: bind() declines with a warning and
+        # fused() hands back the same matrix through the library collective
+        if len({b - a for a, b in (ckb.shard_rows(n_out, world, r) for r in range(world))}) == 1:
+            import warnings
+
+            class FullGroup:      # the part of PeerGroup that bind() consults, with no room left
+                world, mapped_bytes, map_limit_bytes = 2, 10 << 30, 10 << 30
+
+                def fits(self, nbytes):
+                    return False
+
+                def alloc(self, nbytes):
+                    raise AssertionError("bind() must not allocate beyond the limit")
+
+            with warnings.catch_warnings(record=True) as caught:
+                warnings.simplefilter("always")
+                assert lin.bind(FullGroup(), 48) is None
+            assert any("NCCL all-gather" in str(wn.message) for wn in caught)
+            assert torch.equal(lin.fused(x), y)
         np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([1]))
     finally:
         dist.destroy_process_group()
