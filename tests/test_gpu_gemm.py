@@ -288,6 +288,55 @@ def test_weight_loads_ahead_of_the_preceding_kernel(mnk, variant_under_promise, 
     assert ckb.read_device_status() == 0
 
 
+def test_short_row_configurations_on_random_problems(ckb):
+    """Random small-M problems (M <= 64; N any multiple of 8, K any multiple of 32, so tiles, bands of scales, K stages and
+    the ranks of a cluster all meet ragged edges), every output and bias dtype, alpha in place of the two tensor scales:
+    the 64-column tiles and the cluster split, with and without weight loads ahead of the preceding kernel, against
+    the 128-column tiles - bit for bit when K is cut into the same number of splits, within 1e-3 relative RMS
+    otherwise (the order in which fp32 partial sums are added differs)."""
+    import random
+
+    from comfy_kitchen_b200 import _lib
+    L = _lib.load()
+    rng = random.Random(1234)
+    dtypes = [torch.bfloat16, torch.float16, torch.float32]
+    prev = ckb.set_tuning(1, 0)
+    try:
+        for case in range(36):
+            M = rng.choice([1, 3, 16, 17, 31, 32, 33, 48, 64])
+            N = 8 * rng.randint(1, 400)
+            K = 32 * rng.randint(1, 160)
+            x, w, qx, sfx, tsx, qw, sfw, tsw = quantized_operands(ckb, M, N, K, seed=1000 + case)
+            out_dtype = dtypes[case % 3]
+            bias = None
+            if case % 4:
+                bias = seeded_randn((1, N), seed=case, std=0.5).reshape(N).cuda().to(dtypes[(case // 3) % 2])
+            alpha = (tsx * tsw * 0.5).reshape(()) if case % 5 == 0 else None
+            kw = dict(bias=bias, out_dtype=out_dtype, alpha=alpha)
+            ckb.set_tuning(1, 1)
+            ref = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, **kw)
+            splits_ref = L.ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
+            torch.cuda.synchronize()
+            for variant in (5, 6):
+                for promise in (False, True):
+                    ckb.set_tuning(1, variant)
+                    was = ckb.promise_resident_weights(promise)
+                    try:
+                        y = ckb.scaled_mm_nvfp4(qx, qw, tsx, tsw, sfx, sfw, **kw)
+                        splits = L.ck_b200_query(_lib.QUERY_LAST_GEMM_SPLITS)
+                    finally:
+                        ckb.promise_resident_weights(was)
+                    what = f"case {case}: M={M} N={N} K={K} variant {variant} promise {promise} splits {splits}/{splits_ref}"
+                    assert y.shape == ref.shape and y.dtype == ref.dtype, what
+                    if splits == splits_ref:
+                        assert torch.equal(y, ref), what
+                    else:
+                        assert rel_rms(y[:M].float(), ref[:M].float()) <= 1e-3, what
+    finally:
+        ckb.set_tuning(1, prev)
+    assert ckb.read_device_status() == 0
+
+
 EXACT = [(4608, 9216, 3072), (4608, 4608, 3072), (4608, 6144, 3072), (4608, 3072, 12288), (4608, 1536, 3072),
          (32760, 5120, 5120)]
 
